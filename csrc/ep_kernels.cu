@@ -1,0 +1,734 @@
+// Dispatch / combine kernels for sm_100a: stage, plan, pull, push, reduce, barrier.
+// See ep_kernels.hpp for the protocol.  All waits are bounded (prim.cuh); nothing traps.
+#include "ep_kernels.hpp"
+#include "prim.cuh"
+
+namespace nep {
+namespace {
+
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kStageThreads = 512;
+constexpr int kPlanThreads = 256;
+constexpr int kReduceThreads = 512;
+constexpr int kTagStage = 1, kTagPlan = 2, kTagPull = 3, kTagPush = 4, kTagReduce = 5, kTagBarrier = 6;
+
+__device__ __forceinline__ char* window(const CommonParams& c, int r) { return static_cast<char*>(c.peers[r]); }
+__device__ __forceinline__ int* ctrl_words(const CommonParams& c) {
+    return reinterpret_cast<int*>(window(c, c.rank) + c.layout.ctrl_offset);
+}
+__device__ __forceinline__ StatusRef status_of(const CommonParams& c) { return StatusRef{c.status_dev, c.status_host}; }
+__device__ __forceinline__ unsigned lanemask_lt() {
+    unsigned m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+// The block that takes the last ticket runs the tail of a kernel; the counter is reset by it.
+__device__ __forceinline__ bool take_last_ticket(int* ticket) {
+    __shared__ int last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = (atomicAdd(ticket, 1) == int(gridDim.x) - 1);
+    __syncthreads();
+    if (last) __threadfence();
+    return last != 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// stage: copy this rank's tokens (x + gate weights) into its own window, snapshot and count the
+// routing, send the per-destination counts to the peers, peer barrier, derive N / C / offsets.
+// ------------------------------------------------------------------------------------------
+__device__ void stage_body(const StageParams& p) {
+    extern __shared__ int s_counts[];  // [R + E]
+    const WindowLayout& L = p.c.layout;
+    const int R = L.ranks, K = L.topk, H = L.hidden, Le = L.local_experts;
+    const int E = int(L.num_experts);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    char* win = window(p.c, p.c.rank);
+    int* ctrl = ctrl_words(p.c);
+    int* count_acc = ctrl + L.ctrl_count_acc();
+    const StatusRef status = status_of(p.c);
+
+    if (p.fresh) {
+        for (int i = tid; i < R + E; i += blockDim.x) s_counts[i] = 0;
+        __syncthreads();
+    }
+    char* rows = win + L.stage_rows_offset + int64_t(p.parity) * L.stage_rows_stride;
+    int* stage_topk = reinterpret_cast<int*>(win + L.stage_topk_offset + int64_t(p.parity) * L.stage_topk_stride);
+    const int64_t rb = L.row_bytes();
+    const int vecs = H / 8;  // 16-byte chunks per row
+
+    for (int t = gw; t < p.tokens; t += GW) {
+        const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
+        int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
+        for (int i = lane; i < vecs; i += 128) {
+            int4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + j * 32 < vecs) v[j] = ld_nc_v4(src + i + j * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + j * 32 < vecs) dst[i + j * 32] = v[j];
+        }
+        if (lane < K) {
+            const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
+            reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
+        }
+        if (p.fresh) {
+            int e = -1;
+            bool valid = false;
+            if (lane < K) {
+                const int64_t raw = p.topk[int64_t(t) * K + lane];
+                p.snapshot[int64_t(t) * K + lane] = raw;
+                if (raw >= 0 && raw < E) {
+                    e = int(raw);
+                    valid = true;
+                } else if (raw != -1) {
+                    report(status, kBadExpertId, uint32_t(t), kTagStage);
+                }
+                stage_topk[int64_t(t) * K + lane] = e;
+            }
+            const unsigned vmask = __ballot_sync(kFull, valid);
+            const int d = valid ? e / Le : -1;
+            if (valid) {
+                atomicAdd(&s_counts[R + e], 1);
+                const unsigned same = __match_any_sync(vmask, d);
+                if (lane == __ffs(same) - 1) atomicAdd(&s_counts[d], 1);
+            }
+            const unsigned dmask = __reduce_or_sync(kFull, valid ? (1u << d) : 0u);
+            if (lane < R) p.dst_slots[int64_t(t) * R + lane] = ((dmask >> lane) & 1u) ? int64_t(t) : int64_t(-1);
+        }
+    }
+
+    if (p.fresh) {
+        __syncthreads();
+        for (int i = tid; i < R + E; i += blockDim.x)
+            if (s_counts[i] != 0) atomicAdd(&count_acc[i], s_counts[i]);
+    }
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) return;
+
+    // ---- tail: one block per rank
+    const int msg = int(L.msg_ints());
+    if (p.fresh) {
+        for (int i = tid; i < R * msg; i += blockDim.x) {
+            const int d = i / msg, j = i % msg;
+            const int v = j == 0 ? __ldcg(count_acc + d) : j == 1 ? p.tokens : __ldcg(count_acc + R + d * Le + (j - 2));
+            int* remote =
+                reinterpret_cast<int*>(window(p.c, d) + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride) + p.c.rank * msg + j;
+            st_relaxed_sys(remote, v);
+        }
+        for (int d = tid; d < R; d += blockDim.x) p.send_counts[d] = __ldcg(count_acc + d);
+        __syncthreads();
+        for (int i = tid; i < R + E; i += blockDim.x) count_acc[i] = 0;
+    }
+    if (tid == 0) ctrl[WindowLayout::kTicketStage] = 0;
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_ok;
+    if (warp == 0) {
+        const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagStage);
+        if (lane == 0) s_ok = ok;
+    }
+    __syncthreads();
+    if (!p.fresh) return;
+    if (!s_ok) {
+        if (tid == 0) {
+            p.mailbox[1] = -2;
+            p.mailbox[0] = -2;
+            __threadfence_system();
+        }
+        return;
+    }
+    const int* in = reinterpret_cast<const int*>(win + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride);
+    __shared__ int s_total[2];
+    if (warp == 0) {
+        // receive rows by source: inclusive prefix (R <= 32)
+        const int n = lane < R ? ld_relaxed_sys(in + lane * msg) : 0;
+        const int incl = warp_inclusive_sum(n);
+        if (lane < R) {
+            p.recv_rank_prefix[lane] = incl;
+            ctrl[L.ctrl_recv_prefix() + lane] = incl - n;
+            ctrl[L.ctrl_src_tokens() + lane] = ld_relaxed_sys(in + lane * msg + 1);
+            ctrl[L.ctrl_row_cursor() + lane] = 0;
+        }
+        if (lane == R - 1) {
+            ctrl[L.ctrl_recv_prefix() + R] = incl;
+            s_total[0] = incl;
+        }
+    } else if (warp == 1) {
+        // per local expert: sum over sources, round up to the alignment, exclusive scan in waves of 32
+        int carry = 0;
+        for (int base = 0; base < Le; base += 32) {
+            const int l = base + lane;
+            int cnt = 0;
+            if (l < Le)
+                for (int s = 0; s < R; ++s) cnt += ld_relaxed_sys(in + s * msg + 2 + l);
+            const int padded = (cnt + p.alignment - 1) / p.alignment * p.alignment;
+            const int incl = warp_inclusive_sum(padded);
+            if (l < Le) {
+                const int off = carry + incl - padded;
+                p.expert_counts[l] = cnt;
+                p.expert_offsets[l] = off;
+                ctrl[L.ctrl_expert_counts() + l] = cnt;
+                ctrl[L.ctrl_expert_offsets() + l] = off;
+                ctrl[L.ctrl_expert_cursor() + l] = 0;
+            }
+            carry += __shfl_sync(kFull, incl, 31);
+        }
+        if (lane == 0) {
+            p.expert_offsets[Le] = carry;
+            ctrl[L.ctrl_expert_offsets() + Le] = carry;
+            s_total[1] = carry;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence_system();
+        p.mailbox[1] = s_total[1];
+        p.mailbox[0] = s_total[0];
+        __threadfence_system();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// plan (fresh dispatch): every receiver scans all sources' staged routing in chunks of 32 tokens,
+// keeps the tokens that chose one of its experts, and assigns a receive row (grouped by source
+// rank) and, in the expert-major layout, one slot per local choice.
+// ------------------------------------------------------------------------------------------
+__device__ void plan_body(const PlanParams& p) {
+    extern __shared__ int s_chunk[];  // [warps][32*K]
+    const WindowLayout& L = p.c.layout;
+    const int R = L.ranks, K = L.topk, Le = L.local_experts;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    int* ctrl = ctrl_words(p.c);
+    const int* prefix = ctrl + L.ctrl_recv_prefix();
+    const int* src_tokens = ctrl + L.ctrl_src_tokens();
+    const int* eoff = ctrl + L.ctrl_expert_offsets();
+    int* row_cursor = ctrl + L.ctrl_row_cursor();
+    int* expert_cursor = ctrl + L.ctrl_expert_cursor();
+    int* meta = reinterpret_cast<int*>(window(p.c, p.c.rank) + L.meta_scratch_offset);
+    int* mine = s_chunk + warp * 32 * K;
+    const StatusRef status = status_of(p.c);
+    const int cps = int((L.max_tokens + 31) / 32);
+    const int lo = p.c.rank * Le;
+
+    for (int c = gw; c < R * cps; c += GW) {
+        const int s = c / cps, tok0 = (c % cps) * 32;
+        const int Ts = src_tokens[s];
+        if (tok0 >= Ts) continue;
+        const int n_tok = min(32, Ts - tok0);
+        const int n = n_tok * K;
+        const int* remote =
+            reinterpret_cast<const int*>(window(p.c, s) + L.stage_topk_offset + int64_t(p.parity) * L.stage_topk_stride) + int64_t(tok0) * K;
+        __syncwarp();
+        for (int base = 0; base < n; base += 256) {
+            int v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + j * 32 + lane;
+                v[j] = i < n ? ld_relaxed_sys(remote + i) : -1;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + j * 32 + lane;
+                if (i < n) mine[i] = v[j];
+            }
+        }
+        __syncwarp();
+        bool has = false;
+        if (lane < n_tok)
+            for (int k = 0; k < K; ++k) {
+                const int e = mine[lane * K + k];
+                has |= (e >= lo && e < lo + Le);
+            }
+        const unsigned hm = __ballot_sync(kFull, has);
+        if (hm == 0) continue;
+        int base_row = 0;
+        if (lane == 0) base_row = atomicAdd(&row_cursor[s], __popc(hm));
+        base_row = __shfl_sync(kFull, base_row, 0);
+        if (has) {
+            const int row = prefix[s] + base_row + __popc(hm & lanemask_lt());
+            if (row >= prefix[s + 1]) {
+                report(status, kSlotOverflow, uint32_t(row), kTagPlan);
+            } else {
+                int* m = meta + int64_t(row) * (K + 2);
+                m[0] = s;
+                m[1] = tok0 + lane;
+                for (int k = 0; k < K; ++k) {
+                    const int e = mine[lane * K + k];
+                    int v = -1;
+                    if (e >= lo && e < lo + Le) {
+                        const int le = e - lo;
+                        if (p.expand) {
+                            v = eoff[le] + atomicAdd(&expert_cursor[le], 1);
+                            if (v >= eoff[le + 1]) {
+                                report(status, kSlotOverflow, uint32_t(v), kTagPlan);
+                                v = -1;
+                            }
+                        } else {
+                            v = le;
+                        }
+                    }
+                    m[2 + k] = v;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Ring of row buffers private to one warp, filled by bulk loads that complete on mbarriers.
+// ------------------------------------------------------------------------------------------
+struct Ring {
+    char* buf;
+    uint64_t* bars;
+    int stages;
+    int64_t pitch;
+    __device__ __forceinline__ char* slot(int i) const { return buf + int64_t(i % stages) * pitch; }
+    __device__ __forceinline__ uint64_t* bar(int i) const { return bars + (i % stages); }
+    __device__ __forceinline__ uint32_t phase(int i) const { return uint32_t(i / stages) & 1u; }
+};
+
+__device__ __forceinline__ Ring make_ring(char* smem, int warps, int stages, int64_t row_bytes) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t pitch = align_up(row_bytes, 128);
+    Ring r;
+    r.buf = smem + int64_t(warp) * stages * pitch;
+    r.bars = reinterpret_cast<uint64_t*>(smem + int64_t(warps) * stages * pitch) + warp * stages;
+    r.stages = stages;
+    r.pitch = pitch;
+    if (lane == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(r.bars + s, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------
+// pull: for every receive row, bulk-load the staged row from its source rank (NVLink or local)
+// into shared memory and bulk-store it to its final place(s): row r (compact) or every
+// expert-major slot of the row (expanded).  Gaps of the expert-major layout are zero-filled here.
+// ------------------------------------------------------------------------------------------
+__device__ void pull_body(const PullParams& p) {
+    extern __shared__ __align__(128) char s_ring[];
+    const WindowLayout& L = p.c.layout;
+    const int R = L.ranks, K = L.topk, H = L.hidden, Le = L.local_experts;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    const int64_t rb = L.row_bytes();
+    const StatusRef status = status_of(p.c);
+    const int MW = K + 2;
+    Ring ring = make_ring(s_ring, wpb, p.stages, rb);
+    const int S = p.stages;
+    const int n_my = p.rows > gw ? (p.rows - gw + GW - 1) / GW : 0;
+
+    auto issue = [&](int i) {
+        if (lane == 0) {
+            const int r = gw + i * GW;
+            int src = p.meta[int64_t(r) * MW], tok = p.meta[int64_t(r) * MW + 1];
+            if (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens) {
+                report(status, kBadMetadata, uint32_t(r), kTagPull);
+                src = p.c.rank;
+                tok = 0;
+            }
+            const char* from = window(p.c, src) + L.stage_rows_offset + int64_t(p.parity) * L.stage_rows_stride + int64_t(tok) * rb;
+            mbar_expect_tx(ring.bar(i), uint32_t(rb));
+            bulk_load(ring.slot(i), from, uint32_t(rb), ring.bar(i));
+        }
+    };
+    for (int i = 0; i < min(S - 1, n_my); ++i) issue(i);
+
+    // Gaps between an expert's last real row and the next expert's first slot.
+    if (p.expand) {
+        const int vecs = H / 8;
+        int base = 0;
+        for (int l = 0; l < Le; ++l) {
+            const int gs = int(p.expert_offsets[l] + p.expert_counts[l]);
+            const int len = int(p.expert_offsets[l + 1]) - gs;
+            int first = (gw - base) % GW;
+            if (first < 0) first += GW;
+            for (int j = first; j < len; j += GW) {
+                const int64_t row = gs + j;
+                if (p.zero_padding) {
+                    int4* dst = reinterpret_cast<int4*>(p.x_out + row * H);
+                    for (int i = lane; i < vecs; i += 32) dst[i] = make_int4(0, 0, 0, 0);
+                    if (lane == 0 && p.w_out != nullptr) p.w_out[row] = 0.f;
+                }
+                if (lane == 0 && p.slot_map != nullptr) p.slot_map[row] = -1;
+            }
+            base = (base + len) % GW;
+        }
+    }
+
+    for (int i = 0; i < n_my; ++i) {
+        bool ok = mbar_wait(ring.bar(i), ring.phase(i), p.c.timeout_ns);
+        ok = __all_sync(kFull, ok);
+        if (!ok) {
+            if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPull);
+            break;
+        }
+        const int r = gw + i * GW;
+        const int* m = p.meta + int64_t(r) * MW;
+        const int v = lane < K ? m[2 + lane] : -1;
+        const char* st = ring.slot(i);
+        const float* st_w = reinterpret_cast<const float*>(st + wire_weights_offset(H));
+        if (p.expand) {
+            if (v >= 0) {
+                bulk_store(p.x_out + int64_t(v) * H, st, uint32_t(H) * 2u);
+                if (p.w_out != nullptr) p.w_out[v] = st_w[lane];
+                if (p.slot_map != nullptr) p.slot_map[v] = r * K + lane;
+            }
+        } else {
+            if (lane == 0) bulk_store(p.x_out + int64_t(r) * H, st, uint32_t(H) * 2u);
+            if (lane < K) {
+                p.topk_out[int64_t(r) * K + lane] = v;
+                if (p.w_out != nullptr) p.w_out[int64_t(r) * K + lane] = st_w[lane];
+            }
+        }
+        if (p.write_meta) {
+            for (int j = lane; j < MW; j += 32) p.meta_out[int64_t(r) * MW + j] = m[j];
+        }
+        bulk_commit();
+        bulk_wait_read<1>();
+        __syncwarp();
+        if (i + S - 1 < n_my) issue(i + S - 1);
+    }
+    bulk_wait<0>();
+}
+
+// ------------------------------------------------------------------------------------------
+// push (combine): return expert outputs to the source ranks' partitions.  Tail = peer barrier.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ char* ret_row(const CommonParams& c, int src, int parity, int part, int tok) {
+    const WindowLayout& L = c.layout;
+    return window(c, src) + L.ret_offset + int64_t(parity) * L.ret_stride + (int64_t(part) * L.max_tokens + tok) * L.hidden * 2;
+}
+__device__ __forceinline__ float* ret_w_row(const CommonParams& c, int src, int parity, int tok) {
+    const WindowLayout& L = c.layout;
+    return reinterpret_cast<float*>(window(c, src) + L.ret_w_offset + int64_t(parity) * L.ret_w_stride) + int64_t(tok) * L.topk;
+}
+
+__device__ __forceinline__ void accumulate8(float* acc, const int4& v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+    }
+}
+__device__ __forceinline__ int4 pack8(const float* acc) {
+    int4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    return v;
+}
+
+__device__ void push_body(const PushParams& p) {
+    extern __shared__ __align__(128) char s_ring[];
+    const WindowLayout& L = p.c.layout;
+    const int R = L.ranks, K = L.topk, H = L.hidden;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    const StatusRef status = status_of(p.c);
+    const int MW = K + 2;
+    const uint32_t xb = uint32_t(H) * 2u;
+    Ring ring = make_ring(s_ring, wpb, p.stages, xb);
+    const int S = p.stages;
+    int* ctrl = ctrl_words(p.c);
+
+    auto checked_source = [&](const int* m, int item, int& src, int& tok) {
+        src = m[0];
+        tok = m[1];
+        if (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens) {
+            if (lane == 0) report(status, kBadMetadata, uint32_t(item), kTagPush);
+            return false;
+        }
+        return true;
+    };
+
+    if (p.mode == kPushExpandedReduce) {
+        // FP32 sum of the row's local slots, one bf16 round, one store per (token, this rank).
+        const int vecs = H / 8;
+        const int n_my = p.rows > gw ? (p.rows - gw + GW - 1) / GW : 0;
+        for (int i = 0; i < n_my; ++i) {
+            const int r = gw + i * GW;
+            const int* m = p.meta + int64_t(r) * MW;
+            const int v = lane < K ? m[2 + lane] : -1;
+            const unsigned vm = __ballot_sync(kFull, v >= 0 && v < p.capacity);
+            int src, tok;
+            const bool fine = checked_source(m, r, src, tok) && vm != 0;
+            char* st = ring.slot(i);
+            if (fine) {
+                for (int c = lane; c < vecs; c += 32) {
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    unsigned left = vm;
+                    while (left) {
+                        int k[4];
+                        int4 d[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            k[j] = left ? __ffs(left) - 1 : -1;
+                            if (left) left &= left - 1;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int slot = __shfl_sync(kFull, v, k[j] < 0 ? 0 : k[j]);
+                            if (k[j] >= 0) d[j] = ld_nc_v4(reinterpret_cast<const int4*>(p.y + int64_t(slot) * H) + c);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (k[j] >= 0) accumulate8(acc, d[j]);
+                    }
+                    reinterpret_cast<int4*>(st)[c] = pack8(acc);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                const int part = __ffs(vm) - 1;
+                if (lane == 0) bulk_store(ret_row(p.c, src, p.parity, part, tok), st, xb);
+                if (p.w != nullptr && ((vm >> lane) & 1u)) st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + lane, p.w[v]);
+            }
+            bulk_commit();
+            if (S > 1) bulk_wait_read<1>(); else bulk_wait_read<0>();
+            __syncwarp();
+        }
+    } else {
+        // One bulk load + one bulk store per item (compact: receive row; expanded: slot).
+        const bool by_slot = p.mode == kPushExpanded;
+        const int items = by_slot ? p.capacity : p.rows;
+        const int n_my = items > gw ? (items - gw + GW - 1) / GW : 0;
+        auto live = [&](int item) { return !by_slot || p.slot_map[item] >= 0; };
+        auto issue = [&](int i) {
+            const int item = gw + i * GW;
+            if (lane == 0 && live(item)) {
+                mbar_expect_tx(ring.bar(i), xb);
+                bulk_load(ring.slot(i), p.y + int64_t(item) * H, xb, ring.bar(i));
+            }
+        };
+        for (int i = 0; i < min(S - 1, n_my); ++i) issue(i);
+        for (int i = 0; i < n_my; ++i) {
+            const int item = gw + i * GW;
+            if (live(item)) {
+                bool ok = mbar_wait(ring.bar(i), ring.phase(i), p.c.timeout_ns);
+                ok = __all_sync(kFull, ok);
+                if (!ok) {
+                    if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
+                    break;
+                }
+                int r = item, k_of_slot = 0;
+                if (by_slot) {
+                    const int a = p.slot_map[item];
+                    r = a / K;
+                    k_of_slot = a % K;
+                }
+                int src = 0, tok = 0;
+                const bool in_range = r >= 0 && r < p.rows;
+                const int* m = p.meta + int64_t(in_range ? r : 0) * MW;
+                if (!in_range && lane == 0) report(status, kBadMetadata, uint32_t(item), kTagPush);
+                if (in_range && checked_source(m, item, src, tok)) {
+                    if (by_slot) {
+                        if (lane == 0) {
+                            bulk_store(ret_row(p.c, src, p.parity, k_of_slot, tok), ring.slot(i), xb);
+                            if (p.w != nullptr) st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + k_of_slot, p.w[item]);
+                        }
+                    } else {
+                        const int v = lane < K ? m[2 + lane] : -1;
+                        const unsigned vm = __ballot_sync(kFull, v >= 0);
+                        if (vm != 0) {
+                            if (lane == 0) bulk_store(ret_row(p.c, src, p.parity, __ffs(vm) - 1, tok), ring.slot(i), xb);
+                            if (p.w != nullptr && v >= 0)
+                                st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + lane, p.w[int64_t(r) * K + lane]);
+                        }
+                    }
+                }
+            }
+            bulk_commit();
+            bulk_wait_read<1>();
+            __syncwarp();
+            if (i + S - 1 < n_my) issue(i + S - 1);
+        }
+    }
+    bulk_wait<0>();
+    __threadfence_system();
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketPush)) return;
+    if (threadIdx.x == 0) ctrl[WindowLayout::kTicketPush] = 0;
+    __threadfence_system();
+    __syncthreads();
+    if (warp == 0) peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagPush);
+}
+
+// ------------------------------------------------------------------------------------------
+// reduce (combine): per source token, FP32 sum of the partitions that were written for it,
+// optional bias once, one bf16 round; gate-weight payload restored with masked choices = 0.
+// ------------------------------------------------------------------------------------------
+__device__ void reduce_body(const ReduceParams& p) {
+    const WindowLayout& L = p.c.layout;
+    const int K = L.topk, H = L.hidden, Le = L.local_experts;
+    const int E = int(L.num_experts);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    const char* win = window(p.c, p.c.rank);
+    const char* ret = win + L.ret_offset + int64_t(p.parity) * L.ret_stride;
+    const float* ret_w = reinterpret_cast<const float*>(win + L.ret_w_offset + int64_t(p.parity) * L.ret_w_stride);
+    const int vecs = H / 8;
+    const int64_t part_stride = L.max_tokens * int64_t(H) * 2;
+
+    for (int t = gw; t < p.tokens; t += GW) {
+        const int64_t e = lane < K ? p.topk[int64_t(t) * K + lane] : -1;
+        const bool valid = e >= 0 && e < E;
+        const unsigned vmask = __ballot_sync(kFull, valid);
+        unsigned parts = vmask;
+        if (!p.sum_all_choices) {
+            bool leader = false;
+            if (valid) {
+                const unsigned same = __match_any_sync(vmask, int(e) / Le);
+                leader = lane == __ffs(same) - 1;
+            }
+            parts = __ballot_sync(kFull, leader);
+        }
+        const char* row0 = ret + int64_t(t) * H * 2;
+        for (int c = lane; c < vecs; c += 64) {
+            const bool two = c + 32 < vecs;
+            float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            unsigned left = parts;
+            while (left) {
+                int k[4];
+                int4 d0[4], d1[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    k[j] = left ? __ffs(left) - 1 : -1;
+                    if (left) left &= left - 1;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (k[j] >= 0) {
+                        const int4* src = reinterpret_cast<const int4*>(row0 + k[j] * part_stride);
+                        d0[j] = ld_cg_v4(src + c);
+                        if (two) d1[j] = ld_cg_v4(src + c + 32);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (k[j] >= 0) {
+                        accumulate8(a0, d0[j]);
+                        if (two) accumulate8(a1, d1[j]);
+                    }
+                }
+            }
+            if (p.bias != nullptr) {
+                const int4* b = reinterpret_cast<const int4*>(p.bias + int64_t(t) * H);
+                accumulate8(a0, ld_nc_v4(b + c));
+                if (two) accumulate8(a1, ld_nc_v4(b + c + 32));
+            }
+            int4* out = reinterpret_cast<int4*>(p.out + int64_t(t) * H);
+            out[c] = pack8(a0);
+            if (two) out[c + 32] = pack8(a1);
+        }
+        if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+    }
+}
+
+__device__ void barrier_body(const BarrierParams& p) {
+    peer_barrier_warp(p.c.peers, p.c.rank, p.c.layout.ranks, p.c.layout.signal_offset, p.epoch, p.c.timeout_ns, status_of(p.c),
+                      kTagBarrier);
+}
+
+// ---------------------------------------------------------------- wrappers
+#define NEP_KERNEL_PAIR(name, Params, threads)                                                                  \
+    __global__ void __launch_bounds__(threads) name##_kernel(const __grid_constant__ Params p) { name##_body(p); } \
+    __global__ void __launch_bounds__(threads) name##_multi_kernel(const Params* all) { name##_body(all[blockIdx.y]); }
+
+NEP_KERNEL_PAIR(stage, StageParams, kStageThreads)
+NEP_KERNEL_PAIR(plan, PlanParams, kPlanThreads)
+NEP_KERNEL_PAIR(pull, PullParams, 256)
+NEP_KERNEL_PAIR(push, PushParams, 256)
+NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
+NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
+
+template <typename Params>
+cudaError_t launch_pair(void (*single)(const Params), void (*multi)(const Params*), const Params* params, LaunchShape shape, int threads,
+                        size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(shape.ranks_y > 1 ? (const void*)multi : (const void*)single),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+    }
+    const dim3 grid(shape.grid_x, shape.ranks_y > 1 ? shape.ranks_y : 1);
+    if (shape.ranks_y > 1)
+        multi<<<grid, threads, smem, stream>>>(params);
+    else
+        single<<<grid, threads, smem, stream>>>(*params);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int stage_smem_bytes(const WindowLayout& l) { return int((l.ranks + l.num_experts) * 4); }
+int plan_smem_bytes(const WindowLayout& l) { return (kPlanThreads / 32) * 32 * l.topk * 4; }
+
+RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes) {
+    const int64_t pitch = align_up(row_bytes, 128);
+    RingPlan r{};
+    // The software pipeline needs at least two stages; a row that does not fit twice is rejected
+    // by the caller (warps == 0).
+    r.stages = 3;
+    int64_t budget = int64_t(max_smem_bytes) - 1024;
+    int warps = int(budget / (pitch * r.stages + 8 * r.stages));
+    if (warps < 1) {
+        r.stages = 2;
+        warps = int(budget / (pitch * r.stages + 8 * r.stages));
+    }
+    if (warps < 1) warps = 0;
+    r.warps = warps > 8 ? 8 : warps;
+    r.smem_bytes = size_t(r.warps) * r.stages * (pitch + 8) + 128;
+    return r;
+}
+
+cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream) {
+    return launch_pair<StageParams>(stage_kernel, stage_multi_kernel, params, shape, kStageThreads, smem, stream);
+}
+cudaError_t launch_plan(const PlanParams* params, LaunchShape shape, size_t smem, cudaStream_t stream) {
+    return launch_pair<PlanParams>(plan_kernel, plan_multi_kernel, params, shape, kPlanThreads, smem, stream);
+}
+cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream) {
+    return launch_pair<PullParams>(pull_kernel, pull_multi_kernel, params, shape, warps * 32, smem, stream);
+}
+cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream) {
+    return launch_pair<PushParams>(push_kernel, push_multi_kernel, params, shape, warps * 32, smem, stream);
+}
+cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream) {
+    return launch_pair<ReduceParams>(reduce_kernel, reduce_multi_kernel, params, shape, kReduceThreads, 0, stream);
+}
+cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaStream_t stream) {
+    return launch_pair<BarrierParams>(barrier_kernel, barrier_multi_kernel, params, shape, 32, 0, stream);
+}
+
+int kernel_table(KernelInfo* out, int capacity) {
+    struct Entry {
+        const char* name;
+        const void* fn;
+    };
+    const Entry entries[] = {
+        {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
+        {"push", (const void*)push_kernel},     {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
+    };
+    int n = 0;
+    for (const Entry& e : entries) {
+        if (n >= capacity) break;
+        cudaFuncAttributes a{};
+        if (cudaFuncGetAttributes(&a, e.fn) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+        }
+        out[n++] = KernelInfo{e.name, a.numRegs, int(a.sharedSizeBytes), a.maxThreadsPerBlock, int(a.constSizeBytes)};
+    }
+    return n;
+}
+
+}  // namespace nep

@@ -1,0 +1,139 @@
+// Parameter blocks and launch entry points of the dispatch/combine kernels (torch-free).
+//
+// Every kernel exists as one device body with two __global__ wrappers: the production wrapper
+// takes the parameter block by value for one rank; the multi-rank wrapper reads the block of
+// logical rank blockIdx.y from a device array, so a whole group can run as ONE launch on one GPU
+// (ranks that wait on one another must never be separate launches on the same device).
+//
+// Protocol (differs from the reference's push + epilogue design, csrc/dispatch_main.cuh:356-453):
+//   dispatch = stage (copy tokens into the own window, count, exchange counts, peer barrier)
+//              -> plan (fresh only: receivers scan the sources' routing and assign rows/slots)
+//              -> pull (receivers bulk-load rows from the sources' windows straight into the
+//                 final compact / expert-major output, zero padding included)
+//   combine  = push (expert ranks bulk-store result rows into the sources' return partitions,
+//              optional FP32 local pre-reduction, peer barrier) -> reduce (source-side FP32 sum).
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include "layout.hpp"
+
+namespace nep {
+
+struct CommonParams {
+    void* peers[kMaxRanks];  // window base of every rank as mapped in this process
+    WindowLayout layout;
+    int rank;
+    uint64_t timeout_ns;
+    uint32_t* status_dev;
+    volatile uint32_t* status_host;
+};
+
+struct StageParams {
+    CommonParams c;
+    const __nv_bfloat16* x;   // [T,H]
+    const int64_t* topk;      // [T,K] global expert ids or -1 (fresh only)
+    const float* weights;     // [T,K] or null
+    int tokens;
+    int fresh;
+    int parity;
+    int alignment;
+    uint64_t epoch;
+    // handle tensors written by a fresh dispatch
+    int64_t* snapshot;          // [T,K] copy of topk
+    int64_t* dst_slots;         // [T,R] staging row read by destination d, or -1
+    int64_t* send_counts;       // [R]
+    int64_t* recv_rank_prefix;  // [R] inclusive
+    int64_t* expert_counts;     // [L]
+    int64_t* expert_offsets;    // [L+1]
+    volatile int64_t* mailbox;  // mapped host: [0]=N, [1]=C (negative = failure)
+};
+
+struct PlanParams {
+    CommonParams c;
+    int parity;
+    int expand;
+};
+
+struct PullParams {
+    CommonParams c;
+    const int* meta;  // [N,K+2] plan scratch (fresh) or handle metadata (cached)
+    int rows;
+    int parity;
+    int expand;
+    int zero_padding;
+    int write_meta;
+    int stages;
+    __nv_bfloat16* x_out;
+    int64_t* topk_out;   // compact [N,K]
+    float* w_out;        // compact [N,K] / expanded [C], or null
+    int* meta_out;       // fresh: handle metadata [N,K+2]
+    int* slot_map;       // expanded: [C] -> row*K+k, -1 for padding
+    const int64_t* expert_counts;
+    const int64_t* expert_offsets;
+};
+
+enum PushMode : int { kPushCompact = 0, kPushExpanded = 1, kPushExpandedReduce = 2 };
+
+struct PushParams {
+    CommonParams c;
+    const __nv_bfloat16* y;  // [N,H] or [C,H]
+    const float* w;          // [N,K] or [C] or null
+    const int* meta;         // [N,K+2]
+    const int* slot_map;     // [C] (expanded)
+    int rows;                // N
+    int capacity;            // C
+    int mode;
+    int parity;
+    int stages;
+    uint64_t epoch;
+};
+
+struct ReduceParams {
+    CommonParams c;
+    const int64_t* topk;           // [T,K] source routing snapshot
+    const __nv_bfloat16* bias;     // [T,H] or null
+    __nv_bfloat16* out;            // [T,H]
+    float* w_out;                  // [T,K] or null
+    int tokens;
+    int parity;
+    int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank (first k)
+};
+
+struct BarrierParams {
+    CommonParams c;
+    uint64_t epoch;
+};
+
+struct LaunchShape {
+    int grid_x;
+    int ranks_y;  // 1 = production wrapper, >1 = multi-rank wrapper (params is then a device array)
+};
+
+// Each returns the CUDA error of the launch.  `params` points to one block (ranks_y == 1, host
+// memory) or to a device array of ranks_y blocks.
+cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
+cudaError_t launch_plan(const PlanParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
+cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
+cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
+cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream);
+cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaStream_t stream);
+
+// Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.
+struct RingPlan {
+    int warps, stages;
+    size_t smem_bytes;
+};
+RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes);
+int stage_smem_bytes(const WindowLayout& l);
+int plan_smem_bytes(const WindowLayout& l);
+
+// Table of kernels for diagnostics (name, registers, static smem, max threads), filled from
+// cudaFuncGetAttributes on the current device.
+struct KernelInfo {
+    const char* name;
+    int regs, static_smem, max_threads, const_bytes;
+};
+int kernel_table(KernelInfo* out, int capacity);
+
+}  // namespace nep

@@ -1,0 +1,450 @@
+// Host pipeline: validation, stream choreography, allocation and kernel launches for
+// dispatch() and combine().
+//
+// Same responsibilities as the reference's host pipeline (csrc/pipeline.cu:26-489 plus
+// dispatch_epilogue.cpp / combine_epilogue.cpp): one native call per Python operation; inputs are
+// ordered behind the caller's stream or an explicit event; outputs are allocated with their exact
+// size in the consumer stream's allocator pool; the only host wait is the N/C mailbox of a fresh
+// dispatch.  Every entry point takes a *list* of ranks: one element in production, R elements when a
+// whole logical group shares one GPU (tests) -- then each phase is a single multi-rank launch.
+#include "pipeline.hpp"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <sstream>
+
+namespace nep {
+
+namespace {
+
+void cuda_check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+}
+
+struct DeviceLimits {
+    int sms;
+    int smem_optin;
+};
+DeviceLimits device_limits() {
+    const auto* prop = at::cuda::getCurrentDeviceProperties();
+    return DeviceLimits{prop->multiProcessorCount, int(prop->sharedMemPerBlockOptin)};
+}
+
+void check_payload(const at::Tensor& x, const c10::optional<at::Tensor>& topk, const c10::optional<at::Tensor>& weights,
+                   const WindowLayout& L, int device) {
+    TORCH_CHECK(x.is_cuda() && x.get_device() == device, "x must live on this rank's GPU");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
+    TORCH_CHECK(x.dim() == 2 && x.size(1) == L.hidden, "x must be [T, hidden]");
+    TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+    TORCH_CHECK(x.size(0) <= L.max_tokens, "x has more tokens than num_max_tokens_per_rank");
+    TORCH_CHECK(x.numel() == 0 || reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "x must be 16-byte aligned; clone() an offset view");
+    if (topk.has_value()) {
+        const auto& t = *topk;
+        TORCH_CHECK(t.is_cuda() && t.get_device() == device && t.scalar_type() == at::kLong && t.is_contiguous(),
+                    "topk_idx must be a contiguous int64 tensor on this rank's GPU");
+        TORCH_CHECK(t.dim() == 2 && t.size(0) == x.size(0) && t.size(1) == L.topk, "topk_idx must be [T, num_topk]");
+    }
+    if (weights.has_value()) {
+        const auto& w = *weights;
+        TORCH_CHECK(w.is_cuda() && w.get_device() == device && w.scalar_type() == at::kFloat && w.is_contiguous(),
+                    "weights must be a contiguous float32 tensor on this rank's GPU");
+        TORCH_CHECK(w.dim() == 2 && w.size(0) == x.size(0) && w.size(1) == L.topk, "weights must be [T, num_topk]");
+    }
+}
+
+void check_meta_tensor(const at::Tensor& t, at::ScalarType dtype, at::IntArrayRef shape, int device, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.get_device() == device && t.scalar_type() == dtype && t.is_contiguous() && t.sizes() == shape,
+                "handle metadata '", name, "' has the wrong device, dtype, shape or layout");
+}
+
+// [recv_metadata, expert_counts, expert_offsets, dst_slots, send_counts, topk_idx, recv_rank_prefix, slot_map]
+void check_handle_meta(const std::vector<at::Tensor>& m, const WindowLayout& L, int64_t tokens, bool expand, int64_t capacity, int device) {
+    TORCH_CHECK(m.size() == 8, "handle metadata must hold 8 tensors");
+    const int64_t n = m[0].dim() == 2 ? m[0].size(0) : -1;
+    TORCH_CHECK(n >= 0 && n <= int64_t(L.ranks) * L.max_tokens, "handle receive count out of range");
+    check_meta_tensor(m[0], at::kInt, {n, L.topk + 2}, device, "recv_metadata");
+    check_meta_tensor(m[1], at::kLong, {L.local_experts}, device, "expert_counts");
+    check_meta_tensor(m[2], at::kLong, {L.local_experts + 1}, device, "expert_offsets");
+    check_meta_tensor(m[3], at::kLong, {tokens, L.ranks}, device, "dst_slots");
+    check_meta_tensor(m[4], at::kLong, {L.ranks}, device, "send_counts");
+    check_meta_tensor(m[5], at::kLong, {tokens, L.topk}, device, "topk_idx");
+    check_meta_tensor(m[6], at::kLong, {L.ranks}, device, "recv_rank_prefix");
+    check_meta_tensor(m[7], at::kInt, {expand ? capacity : 0}, device, "slot_map");
+}
+
+// Upload a host array of parameter blocks for a multi-rank launch.  The device buffer comes from the
+// comm stream's pool, so its reuse is ordered behind the launch that reads it.
+template <typename P>
+const P* upload(const std::vector<P>& host, std::vector<at::Tensor>& keep, cudaStream_t stream) {
+    if (host.size() == 1) return host.data();
+    auto buf = at::empty({int64_t(host.size() * sizeof(P))}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA));
+    cuda_check(cudaMemcpyAsync(buf.data_ptr(), host.data(), host.size() * sizeof(P), cudaMemcpyHostToDevice, stream), "parameter upload");
+    keep.push_back(buf);
+    return static_cast<const P*>(buf.data_ptr());
+}
+
+struct Streams {
+    c10::cuda::CUDAStream compute, comm;
+};
+
+Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device) {
+    auto compute = c10::cuda::getCurrentCUDAStream(device);
+    auto comm = c10::cuda::getStreamFromExternal(reinterpret_cast<cudaStream_t>(comm_handle), device);
+    if (previous_event != -1) {
+        cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
+    } else {
+        at::cuda::CUDAEvent ready;
+        ready.record(compute);
+        ready.block(comm);
+    }
+    return Streams{compute, comm};
+}
+
+void validate_group(const std::vector<PeerWindow*>& wins) {
+    TORCH_CHECK(!wins.empty(), "no ranks given");
+    const int n = int(wins.size());
+    TORCH_CHECK(n == 1 || n == wins[0]->world(), "a multi-rank call must cover the whole logical group");
+    for (int i = 0; i < n; ++i) {
+        TORCH_CHECK(wins[i] != nullptr && !wins[i]->closed() && wins[i]->connected(), "peer window is closed or not connected");
+        TORCH_CHECK(n == 1 || wins[i]->rank() == i, "logical ranks must be passed in rank order");
+    }
+}
+
+std::shared_ptr<CompletionEvent> finish(const Streams& s, bool async_op, std::vector<at::Tensor> inputs, std::vector<at::Tensor> results) {
+    if (async_op) {
+        // Inputs were produced on another stream's pool; tell the allocator the comm stream used them.
+        for (auto& t : inputs)
+            if (t.defined() && t.numel() > 0) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), s.comm);
+        auto done = std::make_shared<CompletionEvent>();
+        done->event.record(s.comm);
+        done->protect = std::move(results);
+        return done;
+    }
+    at::cuda::CUDAEvent done;
+    done.record(s.comm);
+    done.block(s.compute);
+    return nullptr;
+}
+
+}  // namespace
+
+void CompletionEvent::wait(const c10::cuda::CUDAStream& stream) {
+    event.block(stream);
+    for (auto& t : protect)
+        if (t.defined() && t.numel() > 0) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), stream);
+}
+void CompletionEvent::current_stream_wait() { wait(c10::cuda::getCurrentCUDAStream()); }
+bool CompletionEvent::query() const { return event.query(); }
+
+DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs,
+                     const std::vector<c10::optional<at::Tensor>>& topks, const std::vector<c10::optional<at::Tensor>>& weights,
+                     const std::vector<std::vector<at::Tensor>>& cached_meta, const std::vector<int64_t>& cached_capacity,
+                     int64_t alignment, bool expand, bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
+                     bool async_op, double mailbox_timeout_s) {
+    validate_group(wins);
+    const int n = int(wins.size());
+    TORCH_CHECK(int(xs.size()) == n && int(topks.size()) == n && int(weights.size()) == n && int(cached_meta.size()) == n &&
+                    int(cached_capacity.size()) == n,
+                "per-rank argument lists must have one entry per rank");
+    const WindowLayout& L = wins[0]->layout();
+    const int device = wins[0]->device();
+    c10::cuda::CUDAGuard device_guard(device);
+    const bool fresh = cached_meta[0].empty();
+    const bool weighted = weights[0].has_value();
+    TORCH_CHECK(alignment > 0 && alignment <= (int64_t(1) << 20), "alignment must be a positive integer");
+    for (int i = 0; i < n; ++i) {
+        TORCH_CHECK(cached_meta[i].empty() == fresh && weights[i].has_value() == weighted, "ranks disagree on cached/weights mode");
+        TORCH_CHECK(fresh == topks[i].has_value(), "fresh dispatch needs topk_idx; cached dispatch uses the handle snapshot");
+        check_payload(xs[i], topks[i], weights[i], L, device);
+        if (!fresh) check_handle_meta(cached_meta[i], L, xs[i].size(0), expand, cached_capacity[i], device);
+        wins[i]->check_status();
+    }
+    const DeviceLimits lim = device_limits();
+    TORCH_CHECK(num_sms >= 1 && num_sms <= lim.sms, "num_sms out of range");
+    const RingPlan ring = plan_ring(L.row_bytes(), lim.smem_optin);
+    TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
+    if (fresh) {
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        cuda_check(cudaStreamIsCapturing(reinterpret_cast<cudaStream_t>(comm_stream), &capture), "capture query");
+        TORCH_CHECK(capture == cudaStreamCaptureStatusNone, "fresh dispatch cannot be captured in a CUDA graph (it waits for counts on the host)");
+    }
+
+    const Streams s = order_inputs(comm_stream, previous_event, device);
+    // Outputs live in the consumer stream's pool: the caller's stream when the call completes on it,
+    // the comm stream when completion is handed over through an event.
+    const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
+    const auto i64 = at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device);
+    const auto i32 = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device);
+    const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device);
+    const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
+
+    DispatchOut out;
+    out.metadata.resize(n);
+    out.outputs.resize(n);
+    out.counts.resize(n);
+    std::vector<at::Tensor> keep;
+    std::vector<StageParams> stage(n);
+    std::vector<int> parity(n);
+    const cudaStream_t cs = s.comm.stream();
+
+    {
+        c10::cuda::CUDAStreamGuard pool(consumer);
+        for (int i = 0; i < n; ++i) {
+            const int64_t T = xs[i].size(0);
+            auto& m = out.metadata[i];
+            if (fresh) {
+                m.resize(8);
+                m[1] = at::empty({L.local_experts}, i64);
+                m[2] = at::empty({L.local_experts + 1}, i64);
+                m[3] = at::empty({T, L.ranks}, i64);
+                m[4] = at::empty({L.ranks}, i64);
+                m[5] = at::empty({T, L.topk}, i64);
+                m[6] = at::empty({L.ranks}, i64);
+            } else {
+                m = cached_meta[i];
+            }
+            parity[i] = wins[i]->next_dispatch_parity();
+            StageParams& p = stage[i];
+            p.c = wins[i]->common();
+            p.x = reinterpret_cast<const __nv_bfloat16*>(xs[i].data_ptr());
+            p.topk = fresh ? topks[i]->data_ptr<int64_t>() : nullptr;
+            p.weights = weighted ? weights[i]->data_ptr<float>() : nullptr;
+            p.tokens = int(T);
+            p.fresh = fresh;
+            p.parity = parity[i];
+            p.alignment = int(alignment);
+            p.epoch = wins[i]->reserve_epochs(1);
+            if (fresh) {
+                p.snapshot = m[5].data_ptr<int64_t>();
+                p.dst_slots = m[3].data_ptr<int64_t>();
+                p.send_counts = m[4].data_ptr<int64_t>();
+                p.recv_rank_prefix = m[6].data_ptr<int64_t>();
+                p.expert_counts = m[1].data_ptr<int64_t>();
+                p.expert_offsets = m[2].data_ptr<int64_t>();
+                wins[i]->arm_mailbox();
+                p.mailbox = wins[i]->mailbox_device();
+            }
+        }
+    }
+    {
+        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        const StageParams* dev = upload(stage, keep, cs);
+        PeerWindow::launches += 1;
+        cuda_check(launch_stage(dev, LaunchShape{int(2 * num_sms), n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
+        if (fresh) {
+            std::vector<PlanParams> plan(n);
+            for (int i = 0; i < n; ++i) {
+                plan[i].c = stage[i].c;
+                plan[i].parity = parity[i];
+                plan[i].expand = expand;
+            }
+            const int chunks = L.ranks * int((L.max_tokens + 31) / 32);
+            const int grid = std::max(1, std::min((chunks + 7) / 8, 4 * lim.sms));
+            const PlanParams* pdev = upload(plan, keep, cs);
+            PeerWindow::launches += 1;
+            cuda_check(launch_plan(pdev, LaunchShape{grid, n}, size_t(plan_smem_bytes(L)), cs), "plan launch");
+        }
+    }
+    for (int i = 0; i < n; ++i) {
+        if (fresh) {
+            std::pair<int64_t, int64_t> nc;
+            {
+                pybind11::gil_scoped_release release;
+                nc = wins[i]->wait_mailbox(cs, mailbox_timeout_s);
+            }
+            out.counts[i] = {nc.first, nc.second};
+        } else {
+            out.counts[i] = {cached_meta[i][0].size(0), cached_capacity[i]};
+        }
+    }
+    std::vector<PullParams> pull(n);
+    {
+        c10::cuda::CUDAStreamGuard pool(consumer);
+        for (int i = 0; i < n; ++i) {
+            const int64_t N = out.counts[i].first, C = out.counts[i].second;
+            auto& m = out.metadata[i];
+            if (fresh) {
+                m[0] = at::empty({N, L.topk + 2}, i32);
+                m[7] = at::empty({expand ? C : 0}, i32);
+            }
+            auto& o = out.outputs[i];
+            o.resize(3);
+            o[0] = at::empty({expand ? C : N, L.hidden}, bf16);
+            o[1] = expand ? at::empty({0}, i64) : at::empty({N, L.topk}, i64);
+            o[2] = !weighted ? at::empty({0}, f32) : expand ? at::empty({C}, f32) : at::empty({N, L.topk}, f32);
+            PullParams& p = pull[i];
+            p.c = stage[i].c;
+            p.meta = fresh ? reinterpret_cast<const int*>(static_cast<char*>(wins[i]->base()) + L.meta_scratch_offset) : m[0].data_ptr<int>();
+            p.rows = int(N);
+            p.parity = parity[i];
+            p.expand = expand;
+            p.zero_padding = zero_padding;
+            p.write_meta = fresh;
+            p.stages = ring.stages;
+            p.x_out = reinterpret_cast<__nv_bfloat16*>(o[0].data_ptr());
+            p.topk_out = expand ? nullptr : o[1].data_ptr<int64_t>();
+            p.w_out = weighted ? o[2].data_ptr<float>() : nullptr;
+            p.meta_out = fresh ? m[0].data_ptr<int>() : nullptr;
+            p.slot_map = (expand && fresh) ? m[7].data_ptr<int>() : nullptr;
+            p.expert_counts = m[1].data_ptr<int64_t>();
+            p.expert_offsets = m[2].data_ptr<int64_t>();
+        }
+    }
+    {
+        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        const PullParams* dev = upload(pull, keep, cs);
+        PeerWindow::launches += 1;
+        cuda_check(launch_pull(dev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "pull launch");
+    }
+    std::vector<at::Tensor> inputs, results;
+    for (int i = 0; i < n; ++i) {
+        inputs.push_back(xs[i]);
+        if (topks[i].has_value()) inputs.push_back(*topks[i]);
+        if (weighted) inputs.push_back(*weights[i]);
+        for (auto& t : out.outputs[i]) results.push_back(t);
+        for (auto& t : out.metadata[i]) results.push_back(t);
+    }
+    out.event = finish(s, async_op, std::move(inputs), std::move(results));
+    return out;
+}
+
+CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs, const std::vector<std::vector<at::Tensor>>& meta,
+                   const std::vector<int64_t>& capacity, const std::vector<c10::optional<at::Tensor>>& weights,
+                   const std::vector<c10::optional<at::Tensor>>& bias, bool expand, bool allow_multiple_reduction, int64_t num_sms,
+                   int64_t comm_stream, int64_t previous_event, bool async_op) {
+    validate_group(wins);
+    const int n = int(wins.size());
+    TORCH_CHECK(int(xs.size()) == n && int(meta.size()) == n && int(capacity.size()) == n && int(weights.size()) == n && int(bias.size()) == n,
+                "per-rank argument lists must have one entry per rank");
+    const WindowLayout& L = wins[0]->layout();
+    const int device = wins[0]->device();
+    c10::cuda::CUDAGuard device_guard(device);
+    const bool weighted = weights[0].has_value();
+    for (int i = 0; i < n; ++i) {
+        const auto& m = meta[i];
+        TORCH_CHECK(m.size() == 8, "handle metadata must hold 8 tensors");
+        const int64_t T = m[5].dim() == 2 ? m[5].size(0) : -1;
+        TORCH_CHECK(T >= 0 && T <= L.max_tokens, "handle source token count out of range");
+        check_handle_meta(m, L, T, expand, capacity[i], device);
+        const int64_t rows = expand ? capacity[i] : m[0].size(0);
+        const auto& x = xs[i];
+        TORCH_CHECK(x.is_cuda() && x.get_device() == device && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2 &&
+                        x.size(0) == rows && x.size(1) == L.hidden,
+                    "combine x must be contiguous CUDA bfloat16 with the handle's exact receive shape");
+        TORCH_CHECK(x.numel() == 0 || reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "combine x must be 16-byte aligned");
+        TORCH_CHECK(weights[i].has_value() == weighted, "ranks disagree on weights presence");
+        if (weighted) {
+            const auto& w = *weights[i];
+            const bool shape_ok = expand ? (w.dim() == 1 && w.size(0) == rows) : (w.dim() == 2 && w.size(0) == rows && w.size(1) == L.topk);
+            TORCH_CHECK(w.is_cuda() && w.get_device() == device && w.scalar_type() == at::kFloat && w.is_contiguous() && shape_ok,
+                        "combine weights must be contiguous CUDA float32 with the handle's receive layout");
+        }
+        if (bias[i].has_value()) {
+            const auto& b = *bias[i];
+            TORCH_CHECK(b.is_cuda() && b.get_device() == device && b.scalar_type() == at::kBFloat16 && b.is_contiguous() && b.dim() == 2 &&
+                            b.size(0) == T && b.size(1) == L.hidden,
+                        "combine bias must be contiguous source [T,H] bfloat16 on this buffer's device");
+            TORCH_CHECK(b.numel() == 0 || reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0, "combine bias must be 16-byte aligned");
+        }
+        wins[i]->check_status();
+    }
+    const DeviceLimits lim = device_limits();
+    TORCH_CHECK(num_sms >= 1 && num_sms <= lim.sms, "num_sms out of range");
+    const RingPlan ring = plan_ring(int64_t(L.hidden) * 2, lim.smem_optin);
+    TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
+
+    const Streams s = order_inputs(comm_stream, previous_event, device);
+    const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
+    const cudaStream_t cs = s.comm.stream();
+    const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device);
+    const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
+
+    CombineOut out;
+    out.outputs.resize(n);
+    std::vector<PushParams> push(n);
+    std::vector<ReduceParams> reduce(n);
+    std::vector<at::Tensor> keep;
+    {
+        c10::cuda::CUDAStreamGuard pool(consumer);
+        for (int i = 0; i < n; ++i) {
+            const auto& m = meta[i];
+            const int64_t T = m[5].size(0);
+            const int parity = wins[i]->next_combine_parity();
+            PushParams& p = push[i];
+            p.c = wins[i]->common();
+            p.y = reinterpret_cast<const __nv_bfloat16*>(xs[i].data_ptr());
+            p.w = weighted ? weights[i]->data_ptr<float>() : nullptr;
+            p.meta = m[0].data_ptr<int>();
+            p.slot_map = expand ? m[7].data_ptr<int>() : nullptr;
+            p.rows = int(m[0].size(0));
+            p.capacity = int(capacity[i]);
+            p.mode = !expand ? kPushCompact : allow_multiple_reduction ? kPushExpandedReduce : kPushExpanded;
+            p.parity = parity;
+            p.stages = ring.stages;
+            p.epoch = wins[i]->reserve_epochs(1);
+            auto& o = out.outputs[i];
+            o.resize(2);
+            o[0] = at::empty({T, L.hidden}, bf16);
+            o[1] = weighted ? at::empty({T, L.topk}, f32) : at::empty({0}, f32);
+            ReduceParams& r = reduce[i];
+            r.c = p.c;
+            r.topk = m[5].data_ptr<int64_t>();
+            r.bias = bias[i].has_value() ? reinterpret_cast<const __nv_bfloat16*>(bias[i]->data_ptr()) : nullptr;
+            r.out = reinterpret_cast<__nv_bfloat16*>(o[0].data_ptr());
+            r.w_out = weighted ? o[1].data_ptr<float>() : nullptr;
+            r.tokens = int(T);
+            r.parity = parity;
+            r.sum_all_choices = (expand && !allow_multiple_reduction) ? 1 : 0;
+        }
+    }
+    {
+        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        const PushParams* pdev = upload(push, keep, cs);
+        PeerWindow::launches += 1;
+        cuda_check(launch_push(pdev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "push launch");
+        const ReduceParams* rdev = upload(reduce, keep, cs);
+        PeerWindow::launches += 1;
+        cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
+    }
+    std::vector<at::Tensor> inputs, results;
+    for (int i = 0; i < n; ++i) {
+        inputs.push_back(xs[i]);
+        if (weighted) inputs.push_back(*weights[i]);
+        if (bias[i].has_value()) inputs.push_back(*bias[i]);
+        for (auto& t : meta[i]) inputs.push_back(t);
+        for (auto& t : out.outputs[i]) results.push_back(t);
+    }
+    out.event = finish(s, async_op, std::move(inputs), std::move(results));
+    return out;
+}
+
+void group_barrier(const std::vector<PeerWindow*>& wins, int64_t stream) {
+    validate_group(wins);
+    const int n = int(wins.size());
+    c10::cuda::CUDAGuard device_guard(wins[0]->device());
+    const cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    if (n == 1) {
+        wins[0]->barrier(cs);
+        return;
+    }
+    std::vector<BarrierParams> b(n);
+    for (int i = 0; i < n; ++i) {
+        b[i].c = wins[i]->common();
+        b[i].epoch = wins[i]->reserve_epochs(1);
+    }
+    std::vector<at::Tensor> keep;
+    c10::cuda::CUDAStreamGuard on(c10::cuda::getStreamFromExternal(cs, wins[0]->device()));
+    const BarrierParams* dev = upload(b, keep, cs);
+    PeerWindow::launches += 1;
+    cuda_check(launch_barrier(dev, LaunchShape{1, n}, cs), "barrier launch");
+}
+
+}  // namespace nep

@@ -1,0 +1,55 @@
+// Host entry points of the native extension (see pipeline.cpp).
+#pragma once
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/util/Optional.h>
+
+#include <memory>
+#include <utility>
+#include <vector>
+
+#include "peer_window.hpp"
+
+namespace nep {
+
+// Completion of an asynchronous operation: an event recorded on the comm stream plus the tensors
+// a consumer stream must be registered with before it may use (and later free) them.  Mirrors the
+// reference's CompletionEvent (csrc/include/nano_ep/event.hpp:12-28).
+struct CompletionEvent {
+    at::cuda::CUDAEvent event;
+    std::vector<at::Tensor> protect;
+    void wait(const c10::cuda::CUDAStream& stream);
+    void current_stream_wait();
+    bool query() const;
+};
+
+struct DispatchOut {
+    // per rank: [x, topk_idx (compact) or empty, topk_weights or empty]
+    std::vector<std::vector<at::Tensor>> outputs;
+    // per rank: [recv_metadata, expert_counts, expert_offsets, dst_slots, send_counts, topk_idx,
+    //            recv_rank_prefix, slot_map]
+    std::vector<std::vector<at::Tensor>> metadata;
+    std::vector<std::pair<int64_t, int64_t>> counts;  // (N, C)
+    std::shared_ptr<CompletionEvent> event;            // null unless async_op
+};
+
+struct CombineOut {
+    std::vector<std::vector<at::Tensor>> outputs;  // per rank: [x, topk_weights or empty]
+    std::shared_ptr<CompletionEvent> event;
+};
+
+DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs,
+                     const std::vector<c10::optional<at::Tensor>>& topks, const std::vector<c10::optional<at::Tensor>>& weights,
+                     const std::vector<std::vector<at::Tensor>>& cached_meta, const std::vector<int64_t>& cached_capacity,
+                     int64_t alignment, bool expand, bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
+                     bool async_op, double mailbox_timeout_s);
+
+CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs, const std::vector<std::vector<at::Tensor>>& meta,
+                   const std::vector<int64_t>& capacity, const std::vector<c10::optional<at::Tensor>>& weights,
+                   const std::vector<c10::optional<at::Tensor>>& bias, bool expand, bool allow_multiple_reduction, int64_t num_sms,
+                   int64_t comm_stream, int64_t previous_event, bool async_op);
+
+void group_barrier(const std::vector<PeerWindow*>& wins, int64_t stream);
+
+}  // namespace nep

@@ -1,0 +1,54 @@
+"""Independent restatement of the window byte layout, for tests.
+
+Deliberately does not import the native layout code: the tests compare this arithmetic with what the
+extension reports (the reference does the same with nano_ep/testing/wire.py:4-25 for its own layout).
+"""
+
+
+def align(value: int, to: int) -> int:
+    return (value + to - 1) // to * to
+
+
+def wire_row_bytes(hidden: int, topk: int) -> int:
+    """bf16 x[H] then fp32 weights[K], padded to a 16-byte multiple."""
+    return align(2 * hidden + 4 * topk, 16)
+
+
+def wire_weights_offset(hidden: int) -> int:
+    return 2 * hidden
+
+
+def count_message_ints(local_experts: int) -> int:
+    return 2 + local_experts
+
+
+def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_experts: int) -> dict:
+    local = num_experts // ranks
+    region = 256
+    at = 0
+
+    def take(nbytes):
+        nonlocal at
+        here = at
+        at = align(at + nbytes, region)
+        return here
+
+    out = {}
+    out["signal_offset"] = take(32 * 8)
+    ctrl_ints = 16 + (ranks + num_experts) + ranks + local + (ranks + 1) + (local + 1) + local + ranks
+    out["ctrl_offset"] = take(ctrl_ints * 4)
+    out["counts_in_stride"] = align(ranks * count_message_ints(local) * 4, region)
+    out["counts_in_offset"] = take(2 * out["counts_in_stride"])
+    out["stage_topk_stride"] = align(max_tokens * topk * 4, region)
+    out["stage_topk_offset"] = take(2 * out["stage_topk_stride"])
+    out["stage_rows_stride"] = align(max_tokens * wire_row_bytes(hidden, topk), region)
+    out["stage_rows_offset"] = take(2 * out["stage_rows_stride"])
+    out["ret_w_stride"] = align(max_tokens * topk * 4, region)
+    out["ret_w_offset"] = take(2 * out["ret_w_stride"])
+    out["ret_stride"] = align(topk * max_tokens * hidden * 2, region)
+    out["ret_offset"] = take(2 * out["ret_stride"])
+    out["meta_scratch_offset"] = take(ranks * max_tokens * (topk + 2) * 4)
+    out["num_bytes"] = at
+    out["row_bytes"] = wire_row_bytes(hidden, topk)
+    out["msg_ints"] = count_message_ints(local)
+    return out
