@@ -1,0 +1,435 @@
+"""Headline benchmark: expert-parallel dispatch + combine round trip.
+
+Metric and configuration follow the reference's DeepSeek-V3-shape target: 4096 tokens per rank x hidden
+7168 bf16, top-8 of 256 experts (contiguous placement), softmax top-k routing, expert-major layout
+with zero padding, fresh dispatch followed by combine.  One process per GPU; weak scaling (tokens
+per rank fixed).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints ONE JSON line.  ``value`` is the whole-job payload rate in GB/s: per step every rank
+receives N deduplicated rows in dispatch and C_valid assignment rows come back in combine; bytes =
+(sum over ranks of N + C_valid) * hidden * 2, divided by the slowest rank's device time per step.
+
+Arms: ``--impl ours`` (default), ``--impl nccl`` (torch.distributed all_to_all_single + index ops, a
+baseline), ``--impl reference`` (the reference package; not installable offline, prints why).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from datetime import timedelta
+
+REFERENCE_UNAVAILABLE = (
+    "reference cannot be installed offline: its setup.py requires the DeepJIT submodule (third-party/deep_jit), "
+    "which is empty in the mounted checkout, and its kernels are only reachable through that JIT"
+)
+
+
+def parse_args():
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
+    p.add_argument("--tokens", type=int, default=4096)
+    p.add_argument("--hidden", type=int, default=7168)
+    p.add_argument("--experts", type=int, default=256)
+    p.add_argument("--topk", type=int, default=8)
+    p.add_argument("--alignment", type=int, default=128)
+    p.add_argument("--layout", choices=("expanded", "compact"), default="expanded")
+    p.add_argument("--routing", choices=("balanced", "zipf", "uniform"), default="balanced")
+    p.add_argument("--cached", action="store_true", help="reuse the routing handle after the first step")
+    p.add_argument("--multiple-reduction", action="store_true")
+    p.add_argument("--num-sms", type=int, default=None)
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--detail", action="store_true", help="also time dispatch and combine separately")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.gpu_index)],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                if out:
+                    self.samples.append([f.strip() for f in out.splitlines()[0].split(",")])
+            except Exception:  # noqa: BLE001 - sampling is best effort
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[1]))
+                mx.append(float(s[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[4:8]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples": len(sm),
+        }
+
+
+def make_inputs(args, rank, world, device):
+    import torch
+
+    from nanoep_b200.testing.cases import balanced_routing, uniform_routing, zipf_routing
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    x = torch.randn(args.tokens, args.hidden, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    if args.routing == "balanced":
+        idx, w = balanced_routing(args.tokens, args.experts, args.topk, seed=99 + rank)
+    elif args.routing == "zipf":
+        idx, w = zipf_routing(args.tokens, args.experts, args.topk, seed=99 + rank)
+    else:
+        idx, w = uniform_routing(args.tokens, args.experts, args.topk, seed=99 + rank)
+    return x.pin_memory(), idx.pin_memory(), w.pin_memory()
+
+
+def run_ours(args, rank, world, device, control_group):
+    import torch
+    import torch.distributed as dist
+
+    from nanoep_b200 import CudaBuffer, EPConfig
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    cfg = EPConfig(args.experts, args.topk, args.hidden, args.tokens)
+    expand = args.layout == "expanded"
+    hx, hidx, hw = make_inputs(args, rank, world, device)
+    x, idx, w = hx.to(device), hidx.to(device), hw.to(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        dist.barrier(group=control_group)
+
+    def max_over_ranks(value: float) -> float:
+        t = torch.tensor([value], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=control_group)
+        return float(t.item())
+
+    def sum_over_ranks(value: float) -> float:
+        t = torch.tensor([value], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=control_group)
+        return float(t.item())
+
+    with CudaBuffer(control_group, cfg, allow_multiple_reduction=args.multiple_reduction) as buf:
+        state = {"handle": None}
+
+        def step(xd, idxd, wd, previous_event=None):
+            handle = state["handle"] if args.cached else None
+            got = buf.dispatch(
+                xd, topk_idx=None if handle is not None else idxd, weights=wd, handle=handle,
+                do_expand=expand if handle is None else None, alignment=args.alignment if handle is None else None,
+                zero_padding=expand, previous_event=previous_event, num_sms=args.num_sms,
+            )
+            if args.cached:
+                state["handle"] = got.handle
+            # identity experts: the received rows are returned as they are
+            back = buf.combine(got.x, got.handle, num_sms=args.num_sms)
+            return got, back
+
+        for _ in range(args.warmup):
+            got, back = step(x, idx, w)
+        sync_all()
+        buf.check_status()
+        n_rows = got.handle.layout.recv_count
+        c_valid = int(got.handle.layout.expert_counts.sum().item())
+        c_padded = got.handle.layout.expanded_capacity
+        combine_rows = c_valid if (expand and not args.multiple_reduction) else n_rows
+        recv_from_remote = n_rows - int((got.handle.layout.recv_metadata[:, 0] == rank).sum().item())
+
+        # ---- device-timed steps
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        mids = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        launches_before = ext.launch_count()
+        sync_all()
+        with ClockSampler(device.index) as clocks:
+            wall0 = time.perf_counter()
+            for i in range(args.steps):
+                flush.fill_(i & 0xFF)
+                starts[i].record()
+                handle = state["handle"] if args.cached else None
+                got = buf.dispatch(
+                    x, topk_idx=None if handle is not None else idx, weights=w, handle=handle,
+                    do_expand=expand if handle is None else None, alignment=args.alignment if handle is None else None,
+                    zero_padding=expand, num_sms=args.num_sms,
+                )
+                mids[i].record()
+                back = buf.combine(got.x, got.handle, num_sms=args.num_sms)
+                ends[i].record()
+            sync_all()
+            wall = time.perf_counter() - wall0
+        launches = ext.launch_count() - launches_before
+        buf.check_status()
+        step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        disp_ms = [s.elapsed_time(m) for s, m in zip(starts, mids)]
+        comb_ms = [m.elapsed_time(e) for m, e in zip(mids, ends)]
+        total_ms = max_over_ranks(sum(step_ms))
+        ms_per_step = total_ms / args.steps
+        disp_us = max_over_ranks(statistics.median(disp_ms)) * 1e3
+        comb_us = max_over_ranks(statistics.median(comb_ms)) * 1e3
+        bytes_per_step = sum_over_ranks(float(n_rows + combine_rows)) * args.hidden * 2
+        nvlink_bytes = sum_over_ranks(float(recv_from_remote)) * args.hidden * 2  # dispatch direction only
+        value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+        # ---- end to end: pinned host inputs copied every step (overlapped on a copy stream), result read back
+        e2e = None
+        if not args.no_e2e:
+            copy_stream = torch.cuda.Stream()
+            bufs = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
+            h2d = hx.numel() * 2 + hidx.numel() * 8 + hw.numel() * 4
+
+            def upload(slot):
+                with torch.cuda.stream(copy_stream):
+                    for dst, src in zip(bufs[slot], (hx, hidx, hw)):
+                        dst.copy_(src, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record()
+                return ev
+
+            result_host = torch.empty(1, dtype=torch.float32).pin_memory()
+            for phase, count in (("warm", 2), ("timed", args.steps)):
+                sync_all()
+                t0 = time.perf_counter()
+                ready = upload(0)
+                for i in range(count):
+                    slot = i & 1
+                    nxt = upload(slot ^ 1) if i + 1 < count else None
+                    xd, idxd, wd = bufs[slot]
+                    # the comm stream waits for the copy through previous_event; the caller's stream too
+                    torch.cuda.current_stream().wait_event(ready)
+                    got, back = step(xd, idxd, wd, previous_event=ready)
+                    result_host.copy_(back.x.float().abs().mean().reshape(1), non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+                    _ = float(result_host[0])
+                    copy_stream.wait_stream(torch.cuda.current_stream())
+                    ready = nxt
+                sync_all()
+                elapsed = time.perf_counter() - t0
+            e2e_ms = max_over_ranks(elapsed * 1e3) / args.steps
+            e2e = {
+                "value": bytes_per_step / (e2e_ms * 1e-3) / 1e9,
+                "unit": "GB/s",
+                "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4,
+            }
+        clock_summary = clocks.summary()
+
+    line = {
+        "metric": "ep_dispatch_combine_payload_GBps",
+        "value": value,
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (seeded N(0,1) tokens, softmax top-k routing); no expert weights involved",
+        "impl": "ours",
+        "config": {
+            "model": "DeepSeek-V3 MoE shape: hidden 7168, 256 experts, top-8" if (args.hidden, args.experts, args.topk) == (7168, 256, 8)
+            else f"hidden {args.hidden}, {args.experts} experts, top-{args.topk}",
+            "global_batch": args.tokens * world,
+            "seq_len": args.tokens,
+            "tokens_per_rank": args.tokens,
+            "parallelism": f"ep{world}",
+            "layout": args.layout,
+            "alignment": args.alignment,
+            "zero_padding": expand,
+            "routing": args.routing,
+            "cached_handle": args.cached,
+            "allow_multiple_reduction": args.multiple_reduction,
+            "l2": "256 MiB buffer written between timed steps (outside the timed events); per-step working set ~1.5 GB > 126 MB L2",
+            "value_formula": "(sum_ranks N_dedup_rows + combine_rows) * hidden * 2 B / max_rank device time",
+        },
+        "dispatch_us": disp_us,
+        "combine_us": comb_us,
+        "rows": {"recv_dedup": n_rows, "assignments": c_valid, "padded_capacity": c_padded},
+        "nvlink_dispatch_GBps_per_gpu": (nvlink_bytes / world) / (disp_us * 1e-6) / 1e9 if world > 1 else 0.0,
+        "wall_ms_per_step": max_over_ranks(wall * 1e3) / args.steps,
+        "gpu_launches": launches,
+        "clocks": clock_summary,
+        "e2e": e2e,
+    }
+    return line
+
+
+def run_nccl(args, rank, world, device, control_group):
+    """Baseline: torch.distributed all_to_all_single over NCCL + index ops (sort, index_select, index_add)."""
+    import torch
+    import torch.distributed as dist
+
+    hx, hidx, hw = make_inputs(args, rank, world, device)
+    x, idx, w = hx.to(device), hidx.to(device), hw.to(device)
+    E, K, H, T = args.experts, args.topk, args.hidden, args.tokens
+    L = E // world
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    nccl = dist.group.WORLD
+
+    def dispatch_combine():
+        flat = idx.flatten()
+        token_of = torch.arange(T, device=device).repeat_interleave(K)
+        order = torch.argsort(flat, stable=True)  # expert-major send order
+        send_rows = x[token_of[order]]  # [T*K, H]
+        per_expert = torch.bincount(flat, minlength=E)
+        send_counts = per_expert.view(world, L).sum(1)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=nccl)
+        in_splits, out_splits = send_counts.tolist(), recv_counts.tolist()
+        recv_expert_counts = torch.empty(world * L, dtype=per_expert.dtype, device=device)
+        dist.all_to_all_single(recv_expert_counts, per_expert, group=nccl)
+        recv = torch.empty(sum(out_splits), H, dtype=x.dtype, device=device)
+        dist.all_to_all_single(recv, send_rows, out_splits, in_splits, group=nccl)
+        # expert-major permutation on the receiver (source-major -> expert-major)
+        expert_of = torch.repeat_interleave(torch.arange(L, device=device).repeat(world), recv_expert_counts)
+        perm = torch.argsort(expert_of, stable=True)
+        expert_in = recv[perm]
+        mid = torch.cuda.Event(enable_timing=True)
+        mid.record()
+        # combine: inverse permutation, all_to_all back, weighted-free sum at the source
+        back_rows = torch.empty_like(recv)
+        back_rows[perm] = expert_in
+        returned = torch.empty(T * K, H, dtype=x.dtype, device=device)
+        dist.all_to_all_single(returned, back_rows, in_splits, out_splits, group=nccl)
+        out = torch.zeros(T, H, dtype=torch.float32, device=device)
+        out.index_add_(0, token_of[order], returned.float())
+        return out.to(x.dtype), mid, recv.shape[0]
+
+    for _ in range(args.warmup):
+        dispatch_combine()
+    torch.cuda.synchronize()
+    dist.barrier(group=control_group)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    mids = []
+    with ClockSampler(device.index) as clocks:
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            starts[i].record()
+            _, mid, rows = dispatch_combine()
+            ends[i].record()
+            mids.append(mid)
+        torch.cuda.synchronize()
+        dist.barrier(group=control_group)
+    t = torch.tensor([sum(s.elapsed_time(e) for s, e in zip(starts, ends))], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=control_group)
+    ms_per_step = float(t.item()) / args.steps
+    d = torch.tensor([statistics.median(s.elapsed_time(m) for s, m in zip(starts, mids))], dtype=torch.float64)
+    dist.all_reduce(d, op=dist.ReduceOp.MAX, group=control_group)
+    rows_t = torch.tensor([float(rows)], dtype=torch.float64)
+    dist.all_reduce(rows_t, op=dist.ReduceOp.SUM, group=control_group)
+    bytes_per_step = 2 * float(rows_t.item()) * H * 2
+    return {
+        "metric": "ep_dispatch_combine_payload_GBps",
+        "value": bytes_per_step / (ms_per_step * 1e-3) / 1e9,
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "impl": "nccl_all_to_all_single",
+        "config": {
+            "model": f"hidden {H}, {E} experts, top-{K}", "global_batch": T * world, "seq_len": T, "parallelism": f"ep{world}",
+            "note": "one row per assignment (no per-rank dedup), expert-major permutation by index ops; bytes counted as rows moved each way",
+        },
+        "dispatch_us": float(d.item()) * 1e3,
+        "combine_us": (ms_per_step - float(d.item())) * 1e3,
+        "gpu_launches": 0,
+        "clocks": clocks.summary(),
+    }
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if "RANK" not in os.environ and args.gpus > 1:
+        # convenience: re-launch under torch.distributed.run
+        from nanoep_b200.testing.launcher import free_port
+
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+               "--master-port", str(free_port()), os.path.abspath(__file__)] + sys.argv[1:]
+        return subprocess.call(cmd)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("LOCAL_RANK", str(local_rank))
+    os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, timeout=timedelta(seconds=300), device_id=device)
+    try:
+        control = dist.new_group(backend="gloo", timeout=timedelta(seconds=300))
+        runner = run_ours if args.impl == "ours" else run_nccl
+        line = runner(args, rank, world, device, control)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+    finally:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

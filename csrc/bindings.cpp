@@ -62,7 +62,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                  for (const auto& h : handles) raw.emplace_back(std::string(h));
                  w.import_handles(raw);
              })
-        .def("adopt_peers", &PeerWindow::adopt_peers, py::keep_alive<1, 2>())
+        .def("adopt_peers", &PeerWindow::adopt_peers)
         .def("close_peer_mappings", &PeerWindow::close_peer_mappings)
         .def("close", &PeerWindow::close)
         .def("reserve_epochs", &PeerWindow::reserve_epochs)
@@ -111,6 +111,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
     m.def("group_barrier", &nep::group_barrier);
     m.def("launch_count", [] { return PeerWindow::launches; });
+    m.def("format_status", &nep::format_status);
     m.def("status_name", [](uint32_t code) { return std::string(nep::status_name(code)); });
     m.def("kernel_table", [] {
         nep::KernelInfo info[32];

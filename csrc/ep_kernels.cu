@@ -287,9 +287,18 @@ struct Ring {
     uint64_t* bars;
     int stages;
     int64_t pitch;
+    uint32_t parity;  // bit s = parity of the next phase to wait for on stage s
     __device__ __forceinline__ char* slot(int i) const { return buf + int64_t(i % stages) * pitch; }
     __device__ __forceinline__ uint64_t* bar(int i) const { return bars + (i % stages); }
-    __device__ __forceinline__ uint32_t phase(int i) const { return uint32_t(i / stages) & 1u; }
+    // Wait for the load issued into item i's stage.  Only stages that really received a load may be
+    // waited on: the parity advances per completed wait, not per item, so skipped items are harmless.
+    __device__ __forceinline__ bool wait(int i, uint64_t timeout_ns) {
+        const int s = i % stages;
+        bool ok = mbar_wait(bars + s, (parity >> s) & 1u, timeout_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        parity ^= 1u << s;
+        return ok;
+    }
 };
 
 __device__ __forceinline__ Ring make_ring(char* smem, int warps, int stages, int64_t row_bytes) {
@@ -300,9 +309,11 @@ __device__ __forceinline__ Ring make_ring(char* smem, int warps, int stages, int
     r.bars = reinterpret_cast<uint64_t*>(smem + int64_t(warps) * stages * pitch) + warp * stages;
     r.stages = stages;
     r.pitch = pitch;
+    r.parity = 0;
     if (lane == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(r.bars + s, 1);
         mbar_init_fence();
+        fence_proxy_async_smem();
     }
     __syncwarp();
     return r;
@@ -365,9 +376,7 @@ __device__ void pull_body(const PullParams& p) {
     }
 
     for (int i = 0; i < n_my; ++i) {
-        bool ok = mbar_wait(ring.bar(i), ring.phase(i), p.c.timeout_ns);
-        ok = __all_sync(kFull, ok);
-        if (!ok) {
+        if (!ring.wait(i, p.c.timeout_ns)) {
             if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPull);
             break;
         }
@@ -514,9 +523,7 @@ __device__ void push_body(const PushParams& p) {
         for (int i = 0; i < n_my; ++i) {
             const int item = gw + i * GW;
             if (live(item)) {
-                bool ok = mbar_wait(ring.bar(i), ring.phase(i), p.c.timeout_ns);
-                ok = __all_sync(kFull, ok);
-                if (!ok) {
+                if (!ring.wait(i, p.c.timeout_ns)) {
                     if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
                     break;
                 }

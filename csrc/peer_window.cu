@@ -4,7 +4,7 @@
 #include <chrono>
 #include <cstdio>
 #include <cstring>
-#include <sstream>
+#include <string>
 #include <stdexcept>
 #include <thread>
 
@@ -15,10 +15,9 @@ int64_t PeerWindow::launches = 0;
 namespace {
 void check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
-        std::ostringstream s;
-        s << what << ": " << cudaGetErrorString(e);
+        const std::string message = std::string(what) + ": " + cudaGetErrorString(e);
         cudaGetLastError();
-        throw std::runtime_error(s.str());
+        throw std::runtime_error(message);
     }
 }
 }  // namespace
@@ -206,13 +205,19 @@ std::pair<int64_t, int64_t> PeerWindow::wait_mailbox(cudaStream_t stream, double
     }
 }
 
+std::string format_status(uint32_t code, uint32_t detail, uint32_t tag, int rank) {
+    // snprintf on purpose: numeric operator<< on iostreams is avoided throughout this extension.
+    char buf[320];
+    std::snprintf(buf, sizeof(buf), "nanoep_b200 device status %u (%s), detail %u, kernel tag %u, rank %d", code, status_name(code), detail,
+                  tag, rank);
+    return std::string(buf);
+}
+
 void PeerWindow::check_status() const {
     const uint32_t code = status_host_[0];
     if (code == kOk) return;
-    std::ostringstream s;
-    s << "nanoep_b200 device status " << code << " (" << status_name(code) << "), detail " << status_host_[1] << ", kernel tag "
-      << status_host_[2] << ", rank " << rank_;
-    throw std::runtime_error(s.str());
+    const uint32_t detail = status_host_[1], tag = status_host_[2];
+    throw std::runtime_error(format_status(code, detail, tag, rank_));
 }
 
 void PeerWindow::clear_status(cudaStream_t stream) {

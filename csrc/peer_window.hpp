@@ -87,5 +87,6 @@ private:
 };
 
 const char* status_name(uint32_t code);
+std::string format_status(uint32_t code, uint32_t detail, uint32_t tag, int rank);
 
 }  // namespace nep

@@ -102,7 +102,7 @@ def build_extension(verbose: bool | None = None, force: bool = False):
         extra_include_paths=[str(root)] + cutlass_include_dirs(),
         extra_cflags=["-O2", "-std=c++17"],
         extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", *ARCH_FLAGS],
-        extra_ldflags=["-lcuda"],
+        extra_ldflags=["-lcuda", "-lstdc++", "-lm"],
         build_directory=str(EXT_DIR),
         with_cuda=True,
         verbose=verbose,
@@ -130,3 +130,8 @@ def main():
 
 if __name__ == "__main__":
     main()
+
+
+def build_all(verbose: bool | None = None, force: bool = False):
+    """Build every native artefact of the package (the extension and the stand-alone C libraries)."""
+    return build_extension(verbose=verbose, force=force)
