@@ -134,4 +134,27 @@ if __name__ == "__main__":
 
 def build_all(verbose: bool | None = None, force: bool = False):
     """Build every native artefact of the package (the extension and the stand-alone C libraries)."""
-    return build_extension(verbose=verbose, force=force)
+    module = build_extension(verbose=verbose, force=force)
+    build_noalloc(force=force)
+    return module
+
+
+NOALLOC_LIB = "libnep_noalloc.so"
+
+
+def build_noalloc(force: bool = False) -> Path:
+    """Compile the stand-alone C library with the allocation-free entry point (plain nvcc, no torch)."""
+    import subprocess
+
+    EXT_DIR.mkdir(exist_ok=True)
+    src = source_dir() / "noalloc" / "plan_rows_noalloc.cu"
+    out = EXT_DIR / NOALLOC_LIB
+    stamp = EXT_DIR / (NOALLOC_LIB + ".stamp")
+    digest = hashlib.sha256(src.read_bytes() + (src.parent / "plan_rows_noalloc.h").read_bytes()).hexdigest()
+    if not force and out.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return out
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    cmd = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--compiler-options", "-fPIC", "-shared", "-cudart", "shared", str(src), "-o", str(out)]
+    subprocess.run(cmd, check=True)
+    stamp.write_text(digest)
+    return out
