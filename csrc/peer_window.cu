@@ -90,12 +90,8 @@ void PeerWindow::import_handles(const std::vector<std::string>& handles) {
             check(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
             peers_[p] = mapped;
             imported_[p] = true;
-            cudaPointerAttributes attr{};
-            check(cudaPointerGetAttributes(&attr, mapped), "cudaPointerGetAttributes");
-            if (attr.device == device_) throw std::runtime_error("peer window lives on this rank's own GPU; ranks must use distinct GPUs");
-            int can = 0;
-            check(cudaDeviceCanAccessPeer(&can, device_, attr.device), "cudaDeviceCanAccessPeer");
-            if (!can) throw std::runtime_error("no peer access between the GPUs of this group");
+            // Opening with lazy peer access already fails when the two GPUs cannot reach each other;
+            // that the ranks sit on distinct GPUs is checked by UUID before any handle is exchanged.
         }
     } catch (...) {
         for (int p = 0; p < world_; ++p)

@@ -37,8 +37,9 @@ def free_port() -> int:
 def run_ranks(target: str, nproc: int, *, args=(), log: Path, cwd, timeout: float = 300, env=None, as_module: bool = True) -> tuple[int, str]:
     full_env = dict(os.environ if env is None else env)
     full_env.setdefault("OMP_NUM_THREADS", "1")
-    # Child ranks must not use in-switch multicast: a rank that exits while bound to a multicast
-    # object can fault its peers.
+    full_env["PYTHONPATH"] = os.pathsep.join([str(cwd)] + ([full_env["PYTHONPATH"]] if full_env.get("PYTHONPATH") else []))
+    # Child ranks keep NCCL's in-switch (NVLS) reductions off: a rank that exits while its memory is
+    # bound to such a switch object can fault its peers.
     full_env.setdefault("NCCL_NVLS_ENABLE", "0")
     command = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
