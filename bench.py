@@ -52,7 +52,7 @@ def parse_args():
     p.add_argument("--multiple-reduction", action="store_true")
     p.add_argument("--num-sms", type=int, default=None)
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--detail", action="store_true", help="also time dispatch and combine separately")
+    p.add_argument("--detail", action="store_true", help="record per-kernel device times (median, max over ranks) in phases_us")
     return p.parse_args()
 
 
@@ -186,6 +186,9 @@ def run_ours(args, rank, world, device, control_group):
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         mids = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         launches_before = ext.launch_count()
+        if args.detail:
+            ext.take_phase_timings()
+            ext.set_phase_timing(True)
         sync_all()
         with ClockSampler(device.index) as clocks:
             wall0 = time.perf_counter()
@@ -204,6 +207,13 @@ def run_ours(args, rank, world, device, control_group):
             sync_all()
             wall = time.perf_counter() - wall0
         launches = ext.launch_count() - launches_before
+        phases = None
+        if args.detail:
+            ext.set_phase_timing(False)
+            by_name: dict[str, list[float]] = {}
+            for name, us in ext.take_phase_timings():
+                by_name.setdefault(name, []).append(us)
+            phases = {name: max_over_ranks(statistics.median(v)) for name, v in by_name.items()}
         buf.check_status()
         step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
         disp_ms = [s.elapsed_time(m) for s, m in zip(starts, mids)]
@@ -296,6 +306,7 @@ def run_ours(args, rank, world, device, control_group):
         "nvlink_dispatch_GBps_per_gpu": (nvlink_bytes / world) / (disp_us * 1e-6) / 1e9 if world > 1 else 0.0,
         "wall_ms_per_step": max_over_ranks(wall * 1e3) / args.steps,
         "gpu_launches": launches,
+        "phases_us": phases,
         "clocks": clock_summary,
         "e2e": e2e,
     }

@@ -110,6 +110,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("allow_multiple_reduction"), py::arg("num_sms"), py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"));
 
     m.def("group_barrier", &nep::group_barrier);
+    m.def("set_phase_timing", &nep::set_phase_timing);
+    m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });
     m.def("format_status", &nep::format_status);
     m.def("status_name", [](uint32_t code) { return std::string(nep::status_name(code)); });

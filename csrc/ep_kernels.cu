@@ -319,6 +319,40 @@ __device__ __forceinline__ Ring make_ring(char* smem, int warps, int stages, int
     return r;
 }
 
+
+// Receive rows are stored grouped by source rank.  Walking them in storage order would make every
+// receiver talk to the same source at the same time (one GPU's NVLink port serving all others).
+// Instead item v visits the sources round-robin, starting after the own rank:
+//   source s = (rank + 1 + v % R) % R,  j = v / R,  row = first_row(s) + j   (skipped when j >= rows(s)).
+struct SourceWalk {
+    int first, count;  // lane s: first receive row and row count of source s
+    int items;         // R * max_s count
+    int rank, ranks;
+    __device__ __forceinline__ bool locate(int v, int& row) const {
+        const int s = (rank + 1 + v % ranks) % ranks;
+        const int j = v / ranks;
+        const int f = __shfl_sync(0xffffffffu, first, s);
+        const int c = __shfl_sync(0xffffffffu, count, s);
+        row = f + j;
+        return j < c;
+    }
+};
+__device__ __forceinline__ SourceWalk make_walk(const int64_t* inclusive_prefix, int rank, int ranks) {
+    const int lane = threadIdx.x & 31;
+    SourceWalk w;
+    const int incl = lane < ranks ? int(inclusive_prefix[lane]) : 0;
+    const int prev = lane > 0 && lane < ranks ? int(inclusive_prefix[lane - 1]) : 0;
+    w.first = prev;
+    w.count = lane < ranks ? incl - prev : 0;
+    int mx = w.count;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    w.items = mx * ranks;
+    w.rank = rank;
+    w.ranks = ranks;
+    return w;
+}
+
 // ------------------------------------------------------------------------------------------
 // pull: for every receive row, bulk-load the staged row from its source rank (NVLink or local)
 // into shared memory and bulk-store it to its final place(s): row r (compact) or every
@@ -335,11 +369,13 @@ __device__ void pull_body(const PullParams& p) {
     const int MW = K + 2;
     Ring ring = make_ring(s_ring, wpb, p.stages, rb);
     const int S = p.stages;
-    const int n_my = p.rows > gw ? (p.rows - gw + GW - 1) / GW : 0;
+    const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
+    const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
 
     auto issue = [&](int i) {
-        if (lane == 0) {
-            const int r = gw + i * GW;
+        int r;
+        const bool live = walk.locate(gw + i * GW, r);
+        if (lane == 0 && live) {
             int src = p.meta[int64_t(r) * MW], tok = p.meta[int64_t(r) * MW + 1];
             if (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens) {
                 report(status, kBadMetadata, uint32_t(r), kTagPull);
@@ -376,11 +412,18 @@ __device__ void pull_body(const PullParams& p) {
     }
 
     for (int i = 0; i < n_my; ++i) {
+        int r;
+        if (!walk.locate(gw + i * GW, r)) {
+            bulk_commit();
+            bulk_wait_read<1>();
+            __syncwarp();
+            if (i + S - 1 < n_my) issue(i + S - 1);
+            continue;
+        }
         if (!ring.wait(i, p.c.timeout_ns)) {
             if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPull);
             break;
         }
-        const int r = gw + i * GW;
         const int* m = p.meta + int64_t(r) * MW;
         const int v = lane < K ? m[2 + lane] : -1;
         const char* st = ring.slot(i);
@@ -464,14 +507,16 @@ __device__ void push_body(const PushParams& p) {
     if (p.mode == kPushExpandedReduce) {
         // FP32 sum of the row's local slots, one bf16 round, one store per (token, this rank).
         const int vecs = H / 8;
-        const int n_my = p.rows > gw ? (p.rows - gw + GW - 1) / GW : 0;
+        const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
+        const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
         for (int i = 0; i < n_my; ++i) {
-            const int r = gw + i * GW;
-            const int* m = p.meta + int64_t(r) * MW;
-            const int v = lane < K ? m[2 + lane] : -1;
+            int r;
+            const bool live_row = walk.locate(gw + i * GW, r);
+            const int* m = p.meta + int64_t(live_row ? r : 0) * MW;
+            const int v = (live_row && lane < K) ? m[2 + lane] : -1;
             const unsigned vm = __ballot_sync(kFull, v >= 0 && v < p.capacity);
-            int src, tok;
-            const bool fine = checked_source(m, r, src, tok) && vm != 0;
+            int src = 0, tok = 0;
+            const bool fine = live_row && checked_source(m, r, src, tok) && vm != 0;
             char* st = ring.slot(i);
             if (fine) {
                 for (int c = lane; c < vecs; c += 32) {
@@ -508,21 +553,32 @@ __device__ void push_body(const PushParams& p) {
         }
     } else {
         // One bulk load + one bulk store per item (compact: receive row; expanded: slot).
+        // Expanded: walk the slots (sources are interleaved by the plan's arrival order).
+        // Compact: walk the receive rows round-robin over the sources.
         const bool by_slot = p.mode == kPushExpanded;
-        const int items = by_slot ? p.capacity : p.rows;
+        const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
+        const int items = by_slot ? p.capacity : walk.items;
         const int n_my = items > gw ? (items - gw + GW - 1) / GW : 0;
-        auto live = [&](int item) { return !by_slot || p.slot_map[item] >= 0; };
+        // item index -> (live?, y row to send)
+        auto locate = [&](int v, int& item) {
+            if (by_slot) {
+                item = v;
+                return p.slot_map[v] >= 0;
+            }
+            return walk.locate(v, item);
+        };
         auto issue = [&](int i) {
-            const int item = gw + i * GW;
-            if (lane == 0 && live(item)) {
+            int item;
+            const bool live = locate(gw + i * GW, item);
+            if (lane == 0 && live) {
                 mbar_expect_tx(ring.bar(i), xb);
                 bulk_load(ring.slot(i), p.y + int64_t(item) * H, xb, ring.bar(i));
             }
         };
         for (int i = 0; i < min(S - 1, n_my); ++i) issue(i);
         for (int i = 0; i < n_my; ++i) {
-            const int item = gw + i * GW;
-            if (live(item)) {
+            int item;
+            if (locate(gw + i * GW, item)) {
                 if (!ring.wait(i, p.c.timeout_ns)) {
                     if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
                     break;

@@ -71,6 +71,7 @@ struct PullParams {
     int* slot_map;       // expanded: [C] -> row*K+k, -1 for padding
     const int64_t* expert_counts;
     const int64_t* expert_offsets;
+    const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
 };
 
 enum PushMode : int { kPushCompact = 0, kPushExpanded = 1, kPushExpandedReduce = 2 };
@@ -81,6 +82,7 @@ struct PushParams {
     const float* w;          // [N,K] or [C] or null
     const int* meta;         // [N,K+2]
     const int* slot_map;     // [C] (expanded)
+    const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
     int rows;                // N
     int capacity;            // C
     int mode;

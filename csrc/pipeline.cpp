@@ -29,6 +29,27 @@ void cuda_check(cudaError_t e, const char* what) {
     }
 }
 
+// Optional per-phase device timing: events recorded on the comm stream between launches.  Off by
+// default; switched on from Python for benchmarks (multi-GPU runs cannot use a kernel profiler).
+struct PhaseMarks {
+    bool enabled = false;
+    std::vector<std::pair<std::string, cudaEvent_t>> marks;
+    std::vector<cudaEvent_t> pool;
+    void mark(const char* name, cudaStream_t stream) {
+        if (!enabled) return;
+        cudaEvent_t ev;
+        if (!pool.empty()) {
+            ev = pool.back();
+            pool.pop_back();
+        } else {
+            cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
+        }
+        cuda_check(cudaEventRecord(ev, stream), "cudaEventRecord");
+        marks.emplace_back(name, ev);
+    }
+};
+PhaseMarks g_marks;
+
 struct DeviceLimits {
     int sms;
     int smem_optin;
@@ -237,8 +258,10 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     {
         c10::cuda::CUDAStreamGuard on_comm(s.comm);
         const StageParams* dev = upload(stage, keep, cs);
+        g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
         cuda_check(launch_stage(dev, LaunchShape{int(2 * num_sms), n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
+        g_marks.mark("stage", cs);
         if (fresh) {
             std::vector<PlanParams> plan(n);
             for (int i = 0; i < n; ++i) {
@@ -251,6 +274,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             const PlanParams* pdev = upload(plan, keep, cs);
             PeerWindow::launches += 1;
             cuda_check(launch_plan(pdev, LaunchShape{grid, n}, size_t(plan_smem_bytes(L)), cs), "plan launch");
+            g_marks.mark("plan", cs);
         }
     }
     for (int i = 0; i < n; ++i) {
@@ -296,13 +320,16 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.slot_map = (expand && fresh) ? m[7].data_ptr<int>() : nullptr;
             p.expert_counts = m[1].data_ptr<int64_t>();
             p.expert_offsets = m[2].data_ptr<int64_t>();
+            p.recv_rank_prefix = m[6].data_ptr<int64_t>();
         }
     }
     {
         c10::cuda::CUDAStreamGuard on_comm(s.comm);
         const PullParams* dev = upload(pull, keep, cs);
+        g_marks.mark("host_gap", cs);
         PeerWindow::launches += 1;
         cuda_check(launch_pull(dev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "pull launch");
+        g_marks.mark("pull", cs);
     }
     std::vector<at::Tensor> inputs, results;
     for (int i = 0; i < n; ++i) {
@@ -384,6 +411,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             p.w = weighted ? weights[i]->data_ptr<float>() : nullptr;
             p.meta = m[0].data_ptr<int>();
             p.slot_map = expand ? m[7].data_ptr<int>() : nullptr;
+            p.recv_rank_prefix = m[6].data_ptr<int64_t>();
             p.rows = int(m[0].size(0));
             p.capacity = int(capacity[i]);
             p.mode = !expand ? kPushCompact : allow_multiple_reduction ? kPushExpandedReduce : kPushExpanded;
@@ -408,11 +436,14 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     {
         c10::cuda::CUDAStreamGuard on_comm(s.comm);
         const PushParams* pdev = upload(push, keep, cs);
+        g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
         cuda_check(launch_push(pdev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "push launch");
+        g_marks.mark("push", cs);
         const ReduceParams* rdev = upload(reduce, keep, cs);
         PeerWindow::launches += 1;
         cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
+        g_marks.mark("reduce", cs);
     }
     std::vector<at::Tensor> inputs, results;
     for (int i = 0; i < n; ++i) {
@@ -423,6 +454,24 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
         for (auto& t : out.outputs[i]) results.push_back(t);
     }
     out.event = finish(s, async_op, std::move(inputs), std::move(results));
+    return out;
+}
+
+void set_phase_timing(bool enabled) { g_marks.enabled = enabled; }
+
+std::vector<std::pair<std::string, double>> take_phase_timings() {
+    std::vector<std::pair<std::string, double>> out;
+    auto& m = g_marks.marks;
+    if (!m.empty()) cuda_check(cudaEventSynchronize(m.back().second), "phase timing sync");
+    for (size_t i = 0; i < m.size(); ++i) {
+        if (m[i].first != "begin" && i > 0) {
+            float ms = 0.f;
+            cuda_check(cudaEventElapsedTime(&ms, m[i - 1].second, m[i].second), "cudaEventElapsedTime");
+            out.emplace_back(m[i].first, double(ms) * 1e3);
+        }
+    }
+    for (auto& e : m) g_marks.pool.push_back(e.second);
+    m.clear();
     return out;
 }
 

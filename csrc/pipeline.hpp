@@ -6,6 +6,7 @@
 #include <c10/util/Optional.h>
 
 #include <memory>
+#include <string>
 #include <utility>
 #include <vector>
 
@@ -49,6 +50,10 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
                    const std::vector<int64_t>& capacity, const std::vector<c10::optional<at::Tensor>>& weights,
                    const std::vector<c10::optional<at::Tensor>>& bias, bool expand, bool allow_multiple_reduction, int64_t num_sms,
                    int64_t comm_stream, int64_t previous_event, bool async_op);
+
+// Per-phase device times (name, microseconds) of the operations issued since the last call.
+void set_phase_timing(bool enabled);
+std::vector<std::pair<std::string, double>> take_phase_timings();
 
 void group_barrier(const std::vector<PeerWindow*>& wins, int64_t stream);
 
