@@ -1,0 +1,401 @@
+// Grouped GEMM for expert FFNs on sm_100a: tcgen05.mma with TMEM accumulators, TMA-fed operand
+// tiles, mbarrier pipelines, warp-specialised persistent CTAs.
+//
+//   out[m, :] = epilogue( A[m, :] @ W[e(m)]^T )     for every 128-row block m of the expert-major
+//                                                   activation matrix; e(m) from expert_offsets.
+//
+// The reference library has no GEMM at all (its kernels only move data); this kernel is what lets
+// dispatch feed the expert up-projection and the down-projection feed combine on the same GPU.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+// epilogue (each reads its own quarter of the 128 TMEM lanes).  Tile = 128 x 256 x 64 (bf16, fp32
+// accumulate), 4 shared-memory stages of 48 KB, two 256-column accumulators in TMEM so the epilogue
+// of tile i overlaps the mainloop of tile i+1.
+//
+// Epilogues:
+//   kPlain   : out[128 x 256] = bf16(acc)
+//   kSwiGLU  : the B tile holds 128 gate rows and the 128 matching up rows of the fused [2I, H]
+//              weight; out[128 x 128] = bf16(silu(gate) * up)
+//   kScatter : (fused down-projection + combine) acc * gate weight of the slot -> bf16 -> stored
+//              straight into the source rank's return partition over NVLink (peer pointer).
+// Optional tile gating (fused dispatch + up-projection): the producer waits until the row block's
+// ready counter reaches its expected value before loading A.
+//
+// All waits are bounded; on expiry the CTA records a code in `status`, stops issuing work, still
+// joins the final barrier and frees its TMEM.
+#include "grouped_gemm_sm100.hpp"
+
+#include <cuda_bf16.h>
+
+namespace nep {
+namespace gemm {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;  // 16 KB
+constexpr int kBBytes = BN * BK * 2;  // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kMaxExperts = 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t start = timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try(bar, parity))
+        if ((++spins & 1023u) == 0u && timer_ns() - start > limit_ns) return false;
+    return true;
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
+// 2-D tiled TMA load into this CTA's shared memory (unicast).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
+    const uint32_t addr = smem_u32(tile);
+    uint64_t d = 0;
+    d |= uint64_t((addr >> 4) & 0x3FFF);         // start address / 16
+    d |= uint64_t(1) << 16;                      // leading byte offset (unused for swizzled K-major)
+    d |= uint64_t(1024 >> 4) << 32;              // stride byte offset: next 8-row group
+    d |= uint64_t(1) << 46;                      // descriptor version (sm_100)
+    d |= uint64_t(2) << 61;                      // layout: 128-byte swizzle
+    return d;
+}
+// bf16 x bf16 -> fp32, both operands K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+
+__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct SharedStorage {
+    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int abort;
+    int offsets[kMaxExperts + 1];
+};
+
+__device__ __forceinline__ int find_expert(const int* offsets, int experts, int row) {
+    int lo = 0, hi = experts;  // offsets[lo] <= row < offsets[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (offsets[mid] <= row) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                   const __grid_constant__ CUtensorMap map_b, const Args args) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* tiles = smem;  // kStages x (A 16 KB | B 32 KB), 1024-byte aligned
+    SharedStorage& sh = *reinterpret_cast<SharedStorage*>(smem + kStages * kStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t limit_ns = args.timeout_ns;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&sh.full[s], 1);
+            mbar_init(&sh.empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh.tmem_full[a], 1);
+            mbar_init(&sh.tmem_empty[a], 4);  // one arrival per epilogue warp
+        }
+        sh.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i <= args.num_experts; i += kThreads) sh.offsets[i] = int(args.expert_offsets[i]);
+    if (warp == 1) tmem_alloc(&sh.tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_base;
+
+    const int m_blocks = args.m_blocks, n_tiles = args.n_tiles, k_blocks = args.k_blocks;
+    const int total_tiles = m_blocks * n_tiles;
+    volatile int* abort_flag = &sh.abort;
+
+    auto fail = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (atomicCAS(args.status, 0u, code) == 0u) args.status[1] = blockIdx.x;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const int mb = tile / n_tiles, nt = tile % n_tiles;
+                const int row0 = mb * BM;
+                const int expert = find_expert(sh.offsets, args.num_experts, row0);
+                if (args.tile_ready != nullptr) {
+                    // Rows of this block are written by the dispatch pull of the same GPU; wait for all of them.
+                    const int want = args.tile_expected[mb];
+                    const uint64_t start = timer_ns();
+                    while (ld_acquire_gpu(args.tile_ready + mb) < want) {
+                        __nanosleep(64);
+                        if (timer_ns() - start > limit_ns) {
+                            fail(kGemmTileTimeout);
+                            break;
+                        }
+                    }
+                    if (*abort_flag) break;
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
+                const int b_row0 = expert * args.b_rows_per_expert + (kMode == kSwiGLU ? nt * (BN / 2) : nt * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh.empty[stage], phase ^ 1u, limit_ns)) {
+                        fail(kGemmPipeTimeout);
+                        break;
+                    }
+                    uint8_t* a_dst = tiles + stage * kStageBytes;
+                    uint8_t* b_dst = a_dst + kABytes;
+                    mbar_expect_tx(&sh.full[stage], kStageBytes);
+                    tma_load_2d(a_dst, &map_a, kb * BK, row0, &sh.full[stage]);
+                    if (kMode == kSwiGLU) {
+                        tma_load_2d(b_dst, &map_b, kb * BK, b_row0, &sh.full[stage]);
+                        tma_load_2d(b_dst + kBBytes / 2, &map_b, kb * BK, b_row0 + args.swiglu_up_row_offset, &sh.full[stage]);
+                    } else {
+                        tma_load_2d(b_dst, &map_b, kb * BK, b_row0, &sh.full[stage]);
+                        tma_load_2d(b_dst + kBBytes / 2, &map_b, kb * BK, b_row0 + BN / 2, &sh.full[stage]);
+                    }
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = uint32_t(local >> 1) & 1u;
+                if (!mbar_wait(&sh.tmem_empty[acc], acc_phase ^ 1u, limit_ns)) {
+                    fail(kGemmPipeTimeout);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh.full[stage], phase, limit_ns)) {
+                        fail(kGemmPipeTimeout);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint8_t* a_tile = tiles + stage * kStageBytes;
+                    const uint64_t a_desc = smem_desc_sw128(a_tile);
+                    const uint64_t b_desc = smem_desc_sw128(a_tile + kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+                        tc_mma(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2), kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&sh.empty[stage]);  // frees the stage once these MMAs have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(&sh.tmem_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t acc_phase = uint32_t(local >> 1) & 1u;
+            const int mb = tile / n_tiles, nt = tile % n_tiles;
+            const int row = mb * BM + quarter * 32 + lane;
+            bool ok = mbar_wait(&sh.tmem_full[acc], acc_phase, limit_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) fail(kGemmPipeTimeout);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(acc * BN);
+            if (kMode == kSwiGLU) {
+                __nv_bfloat16* out_row = args.out + int64_t(row) * args.ldo + nt * (BN / 2);
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 16) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + c, g);
+                    tmem_ld16(taddr + BN / 2 + c, u);
+                    tmem_ld_wait();
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float a = silu(__uint_as_float(g[2 * j])) * __uint_as_float(u[2 * j]);
+                        const float b = silu(__uint_as_float(g[2 * j + 1])) * __uint_as_float(u[2 * j + 1]);
+                        o[j] = pack_bf16(a, b);
+                    }
+                    st_v4(out_row + c, o[0], o[1], o[2], o[3]);
+                    st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
+                }
+            } else {
+                // kPlain writes the local output; kScatter scales by the slot's gate weight and writes
+                // into the source rank's return partition (a peer pointer) or skips padding rows.
+                __nv_bfloat16* out_row = nullptr;
+                float scale = 1.f;
+                if (kMode == kPlain) {
+                    out_row = args.out + int64_t(row) * args.ldo + nt * BN;
+                } else {
+                    const int a = args.slot_map[row];
+                    if (a >= 0) {
+                        const int recv_row = a / args.topk, k = a % args.topk;
+                        const int* meta = args.recv_metadata + int64_t(recv_row) * (args.topk + 2);
+                        const int src = meta[0], tok = meta[1];
+                        scale = args.slot_weights != nullptr ? args.slot_weights[row] : 1.f;
+                        out_row = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(args.peers[src]) + args.ret_offset +
+                                                                   (int64_t(k) * args.max_tokens + tok) * int64_t(args.ldo) * 2) +
+                                  nt * BN;
+                    }
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c, v);
+                    tmem_ld_wait();
+                    if (out_row != nullptr) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
+                        st_v4(out_row + c, o[0], o[1], o[2], o[3]);
+                        st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tmem_empty[acc]);
+        }
+        if (kMode == kScatter) __threadfence_system();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+size_t shared_bytes() { return size_t(kStages) * kStageBytes + sizeof(SharedStorage) + 1024; }
+
+template <int kMode>
+cudaError_t launch_mode(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int grid, cudaStream_t stream) {
+    auto* fn = grouped_gemm_kernel<kMode>;
+    const size_t smem = shared_bytes();
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+    fn<<<grid, kThreads, smem, stream>>>(a, b, args);
+    return cudaGetLastError();
+}
+
+cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream) {
+    if (args.num_experts > kMaxExperts) return cudaErrorInvalidValue;
+    switch (mode) {
+        case kPlain: return launch_mode<kPlain>(a, b, args, grid, stream);
+        case kSwiGLU: return launch_mode<kSwiGLU>(a, b, args, grid, stream);
+        case kScatter: return launch_mode<kScatter>(a, b, args, grid, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+int kernel_registers(int mode) {
+    cudaFuncAttributes attr{};
+    const void* fn = mode == kPlain ? (const void*)grouped_gemm_kernel<kPlain>
+                   : mode == kSwiGLU ? (const void*)grouped_gemm_kernel<kSwiGLU>
+                                     : (const void*)grouped_gemm_kernel<kScatter>;
+    if (cudaFuncGetAttributes(&attr, fn) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return attr.numRegs;
+}
+
+}  // namespace gemm
+}  // namespace nep

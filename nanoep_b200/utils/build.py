@@ -30,6 +30,7 @@ SOURCES = (
     "gemm_bindings.cpp",
     "peer_window.cu",
     "ep_kernels.cu",
+    "grouped_gemm_sm100.cu",
 )
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
