@@ -87,14 +87,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         [](const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs, const std::vector<c10::optional<at::Tensor>>& topks,
            const std::vector<c10::optional<at::Tensor>>& weights, const std::vector<std::vector<at::Tensor>>& cached_meta,
            const std::vector<int64_t>& cached_capacity, int64_t alignment, bool expand, bool zero_padding, int64_t num_sms,
-           int64_t comm_stream, int64_t previous_event, bool async_op, double mailbox_timeout_s) {
+           int64_t comm_stream, int64_t previous_event, bool async_op, double mailbox_timeout_s,
+           const std::vector<c10::optional<at::Tensor>>& tile_ready) {
             auto out = nep::dispatch(wins, xs, topks, weights, cached_meta, cached_capacity, alignment, expand, zero_padding, num_sms,
-                                     comm_stream, previous_event, async_op, mailbox_timeout_s);
+                                     comm_stream, previous_event, async_op, mailbox_timeout_s, tile_ready);
             return py::make_tuple(out.outputs, out.metadata, out.counts, out.event);
         },
         py::arg("windows"), py::arg("x"), py::arg("topk_idx"), py::arg("weights"), py::arg("cached_metadata"), py::arg("cached_capacity"),
         py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("num_sms"), py::arg("comm_stream"),
-        py::arg("previous_event"), py::arg("async_op"), py::arg("mailbox_timeout_s") = 60.0);
+        py::arg("previous_event"), py::arg("async_op"), py::arg("mailbox_timeout_s") = 60.0,
+        py::arg("tile_ready") = std::vector<c10::optional<at::Tensor>>{});
 
     m.def(
         "combine",
@@ -109,6 +111,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("windows"), py::arg("x"), py::arg("metadata"), py::arg("capacity"), py::arg("weights"), py::arg("bias"), py::arg("expand"),
         py::arg("allow_multiple_reduction"), py::arg("num_sms"), py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"));
 
+    m.def("combine_finish", &nep::combine_finish);
+    m.def("next_combine_parity", [](PeerWindow& w) { return w.next_combine_parity(); });
     m.def("group_barrier", &nep::group_barrier);
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("take_phase_timings", &nep::take_phase_timings);

@@ -406,16 +406,37 @@ __device__ void pull_body(const PullParams& p) {
                     if (lane == 0 && p.w_out != nullptr) p.w_out[row] = 0.f;
                 }
                 if (lane == 0 && p.slot_map != nullptr) p.slot_map[row] = -1;
+                if (p.tile_ready != nullptr) {
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) red_release_gpu_add(p.tile_ready + int(row / 128), 1);
+                }
             }
             base = (base + len) % GW;
         }
     }
 
+    // With tile counters, a row is announced one iteration late: after the bulk group that stored it
+    // has fully completed (not only been read from shared memory).
+    const bool announce = p.tile_ready != nullptr && p.expand;
+    int announced_slot = -1;
+    auto retire_previous = [&]() {
+        if (announce) {
+            bulk_wait<1>();
+            if (announced_slot >= 0) {
+                fence_proxy_async();
+                red_release_gpu_add(p.tile_ready + announced_slot / 128, 1);
+            }
+        } else {
+            bulk_wait_read<1>();
+        }
+    };
     for (int i = 0; i < n_my; ++i) {
         int r;
         if (!walk.locate(gw + i * GW, r)) {
             bulk_commit();
-            bulk_wait_read<1>();
+            retire_previous();
+            announced_slot = -1;
             __syncwarp();
             if (i + S - 1 < n_my) issue(i + S - 1);
             continue;
@@ -445,11 +466,16 @@ __device__ void pull_body(const PullParams& p) {
             for (int j = lane; j < MW; j += 32) p.meta_out[int64_t(r) * MW + j] = m[j];
         }
         bulk_commit();
-        bulk_wait_read<1>();
+        retire_previous();
+        announced_slot = p.expand ? v : -1;
         __syncwarp();
         if (i + S - 1 < n_my) issue(i + S - 1);
     }
     bulk_wait<0>();
+    if (announce && announced_slot >= 0) {
+        fence_proxy_async();
+        red_release_gpu_add(p.tile_ready + announced_slot / 128, 1);
+    }
 }
 
 // ------------------------------------------------------------------------------------------

@@ -72,6 +72,7 @@ struct PullParams {
     const int64_t* expert_counts;
     const int64_t* expert_offsets;
     const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
+    int* tile_ready;  // optional: [C/128] counters, +1 per expert-major row (data or zero padding) once it is in memory
 };
 
 enum PushMode : int { kPushCompact = 0, kPushExpanded = 1, kPushExpandedReduce = 2 };

@@ -169,7 +169,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
                      const std::vector<c10::optional<at::Tensor>>& topks, const std::vector<c10::optional<at::Tensor>>& weights,
                      const std::vector<std::vector<at::Tensor>>& cached_meta, const std::vector<int64_t>& cached_capacity,
                      int64_t alignment, bool expand, bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
-                     bool async_op, double mailbox_timeout_s) {
+                     bool async_op, double mailbox_timeout_s, const std::vector<c10::optional<at::Tensor>>& tile_ready) {
     validate_group(wins);
     const int n = int(wins.size());
     TORCH_CHECK(int(xs.size()) == n && int(topks.size()) == n && int(weights.size()) == n && int(cached_meta.size()) == n &&
@@ -321,6 +321,14 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.expert_counts = m[1].data_ptr<int64_t>();
             p.expert_offsets = m[2].data_ptr<int64_t>();
             p.recv_rank_prefix = m[6].data_ptr<int64_t>();
+            if (int(tile_ready.size()) == n && tile_ready[i].has_value()) {
+                const auto& t = *tile_ready[i];
+                TORCH_CHECK(expand && zero_padding, "tile counters need the expert-major layout with zero padding");
+                TORCH_CHECK(t.is_cuda() && t.get_device() == device && t.scalar_type() == at::kInt && t.is_contiguous() &&
+                                t.numel() * 128 >= C,
+                            "tile_ready must be a zeroed CUDA int32 tensor with one entry per 128 expert-major rows");
+                p.tile_ready = t.data_ptr<int>();
+            }
         }
     }
     {
@@ -455,6 +463,52 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     }
     out.event = finish(s, async_op, std::move(inputs), std::move(results));
     return out;
+}
+
+std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, const std::vector<std::vector<at::Tensor>>& meta,
+                                       const std::vector<int64_t>& parity, const std::vector<c10::optional<at::Tensor>>& bias) {
+    // Second half of a combine whose push was done by another kernel (the scatter epilogue of the
+    // down-projection GEMM): peer barrier, then the source-side reduction, on the current stream.
+    validate_group(wins);
+    const int n = int(wins.size());
+    TORCH_CHECK(int(meta.size()) == n && int(parity.size()) == n && int(bias.size()) == n, "per-rank argument lists must have one entry per rank");
+    const WindowLayout& L = wins[0]->layout();
+    const int device = wins[0]->device();
+    c10::cuda::CUDAGuard device_guard(device);
+    const cudaStream_t cs = c10::cuda::getCurrentCUDAStream(device).stream();
+    const DeviceLimits lim = device_limits();
+    std::vector<BarrierParams> barrier(n);
+    std::vector<ReduceParams> reduce(n);
+    std::vector<at::Tensor> outs(n), keep;
+    for (int i = 0; i < n; ++i) {
+        TORCH_CHECK(meta[i].size() == 8, "handle metadata must hold 8 tensors");
+        const int64_t T = meta[i][5].size(0);
+        wins[i]->check_status();
+        barrier[i].c = wins[i]->common();
+        barrier[i].epoch = wins[i]->reserve_epochs(1);
+        outs[i] = at::empty({T, L.hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device));
+        ReduceParams& r = reduce[i];
+        r.c = barrier[i].c;
+        r.topk = meta[i][5].data_ptr<int64_t>();
+        if (bias[i].has_value()) {
+            const auto& b = *bias[i];
+            TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.is_contiguous() && b.dim() == 2 && b.size(0) == T &&
+                            b.size(1) == L.hidden,
+                        "bias must be contiguous source [T,H] bfloat16");
+            r.bias = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+        }
+        r.out = reinterpret_cast<__nv_bfloat16*>(outs[i].data_ptr());
+        r.tokens = int(T);
+        r.parity = int(parity[i]);
+        r.sum_all_choices = 1;
+    }
+    const BarrierParams* bdev = upload(barrier, keep, cs);
+    PeerWindow::launches += 1;
+    cuda_check(launch_barrier(bdev, LaunchShape{1, n}, cs), "barrier launch");
+    const ReduceParams* rdev = upload(reduce, keep, cs);
+    PeerWindow::launches += 1;
+    cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
+    return outs;
 }
 
 void set_phase_timing(bool enabled) { g_marks.enabled = enabled; }

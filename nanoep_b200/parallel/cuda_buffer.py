@@ -199,8 +199,14 @@ class CudaBuffer:
         previous_event: torch.cuda.Event | None = None,
         async_op: bool = False,
         num_sms: int | None = None,
+        tile_ready: torch.Tensor | None = None,
     ) -> NativeDispatchResult:
-        """Send every token once to each rank that owns one of its experts; return exact layouts."""
+        """Send every token once to each rank that owns one of its experts; return exact layouts.
+
+        ``tile_ready`` (optional, expert-major layout with zero padding only): a zeroed int32 tensor with
+        one counter per 128 output rows; the pull kernel adds one per row once the row is in memory,
+        so a consumer kernel on another stream can start on a row block as soon as it is complete.
+        """
         check_torch_deterministic()
         if self._closed:
             raise RuntimeError("CudaBuffer is closed")
@@ -229,6 +235,7 @@ class CudaBuffer:
                 -1 if previous_event is None else previous_event.cuda_event,
                 bool(async_op),
                 self._mailbox_timeout_s,
+                [tile_ready],
             )
         if handle is None:
             handle = build_handle(self, metadata[0], counts[0], expand, expert_alignment, x.dtype, main_sms)

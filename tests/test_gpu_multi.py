@@ -34,3 +34,13 @@ def test_example_moe(tmp_path, extra):
     code, text = run_ranks("nanoep_b200.examples.moe", nproc, args=extra, log=tmp_path / "moe.log", cwd=ROOT, timeout=300)
     assert code == 0, text[-4000:]
     assert text.count("NANOEP_MOE_OK=") == nproc, text[-4000:]
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_fused_moe_layer_multi(tmp_path, nproc):
+    if _gpus() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    code, text = run_ranks(str(ROOT / "tests" / "moe_worker.py"), nproc, log=tmp_path / "moe_layer.log", cwd=ROOT, timeout=400, as_module=False)
+    assert code == 0, text[-4000:]
+    for rank in range(nproc):
+        assert f"NANOEP_MOE_LAYER_OK={rank}" in text, text[-4000:]
