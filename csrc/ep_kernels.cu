@@ -60,18 +60,26 @@ __device__ void stage_body(const StageParams& p) {
     const int64_t rb = L.row_bytes();
     const int vecs = H / 8;  // 16-byte chunks per row
 
-    for (int t = gw; t < p.tokens; t += GW) {
+    // Work item = one quarter of a token row, so that even a few thousand tokens spread over the whole
+    // grid and every lane keeps up to eight 16-byte loads in flight.  The warp that takes quarter 0
+    // also handles the token's gate weights and routing.
+    constexpr int kParts = 4;
+    const int per_part = (vecs + kParts - 1) / kParts;
+    for (int item = gw; item < p.tokens * kParts; item += GW) {
+        const int t = item / kParts, q = item % kParts;
         const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
         int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
-        for (int i = lane; i < vecs; i += 128) {
-            int4 v[4];
+        const int end = min(vecs, (q + 1) * per_part);
+        for (int i = q * per_part + lane; i < end; i += 256) {
+            int4 v[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (i + j * 32 < vecs) v[j] = ld_nc_v4(src + i + j * 32);
+            for (int j = 0; j < 8; ++j)
+                if (i + j * 32 < end) v[j] = ld_nc_v4(src + i + j * 32);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (i + j * 32 < vecs) dst[i + j * 32] = v[j];
+            for (int j = 0; j < 8; ++j)
+                if (i + j * 32 < end) dst[i + j * 32] = v[j];
         }
+        if (q != 0) continue;
         if (lane < K) {
             const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
             reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
@@ -257,22 +265,29 @@ __device__ void plan_body(const PlanParams& p) {
                 int* m = meta + int64_t(row) * (K + 2);
                 m[0] = s;
                 m[1] = tok0 + lane;
-                for (int k = 0; k < K; ++k) {
-                    const int e = mine[lane * K + k];
-                    int v = -1;
-                    if (e >= lo && e < lo + Le) {
-                        const int le = e - lo;
-                        if (p.expand) {
-                            v = eoff[le] + atomicAdd(&expert_cursor[le], 1);
-                            if (v >= eoff[le + 1]) {
+                // Eight choices at a time: all slot atomics of a group are issued before any result
+                // is consumed, so their latencies overlap.
+                for (int k0 = 0; k0 < K; k0 += 8) {
+                    int le[8], got[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int e = k0 + j < K ? mine[lane * K + k0 + j] : -1;
+                        le[j] = (e >= lo && e < lo + Le) ? e - lo : -1;
+                        got[j] = (p.expand && le[j] >= 0) ? atomicAdd(&expert_cursor[le[j]], 1) : 0;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (k0 + j >= K) break;
+                        int v = -1;
+                        if (le[j] >= 0) {
+                            v = p.expand ? eoff[le[j]] + got[j] : le[j];
+                            if (p.expand && v >= eoff[le[j] + 1]) {
                                 report(status, kSlotOverflow, uint32_t(v), kTagPlan);
                                 v = -1;
                             }
-                        } else {
-                            v = le;
                         }
+                        m[2 + k0 + j] = v;
                     }
-                    m[2 + k] = v;
                 }
             }
         }
