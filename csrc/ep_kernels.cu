@@ -10,6 +10,7 @@ constexpr unsigned kFull = 0xffffffffu;
 constexpr int kStageThreads = 512;
 constexpr int kPlanThreads = 256;
 constexpr int kReduceThreads = 512;
+constexpr int kZeroBytes = 2048;  // zero source of the padding rows
 constexpr int kTagStage = 1, kTagPlan = 2, kTagPull = 3, kTagPush = 4, kTagReduce = 5, kTagBarrier = 6;
 
 __device__ __forceinline__ char* window(const CommonParams& c, int r) { return static_cast<char*>(c.peers[r]); }
@@ -69,7 +70,7 @@ __device__ void stage_body(const StageParams& p) {
         const int t = item / kParts, q = item % kParts;
         const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
         int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
-        const int end = min(vecs, (q + 1) * per_part);
+        const int end = p.skip_copy ? 0 : min(vecs, (q + 1) * per_part);
         for (int i = q * per_part + lane; i < end; i += 256) {
             int4 v[8];
 #pragma unroll
@@ -151,6 +152,18 @@ __device__ void stage_body(const StageParams& p) {
     }
     const int* in = reinterpret_cast<const int*>(win + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride);
     __shared__ int s_total[2];
+    // Phase 1 (all threads): per local expert, sum the sources' counts and round up to the alignment.
+    // The padded sizes reuse the dynamic shared array (R + E ints >= L ints).
+    int* s_padded = s_counts;
+    for (int l = tid; l < Le; l += blockDim.x) {
+        int cnt = 0;
+        for (int src = 0; src < R; ++src) cnt += ld_relaxed_sys(in + src * msg + 2 + l);
+        p.expert_counts[l] = cnt;
+        ctrl[L.ctrl_expert_counts() + l] = cnt;
+        ctrl[L.ctrl_expert_cursor() + l] = 0;
+        s_padded[l] = (cnt + p.alignment - 1) / p.alignment * p.alignment;
+    }
+    __syncthreads();
     if (warp == 0) {
         // receive rows by source: inclusive prefix (R <= 32)
         const int n = lane < R ? ld_relaxed_sys(in + lane * msg) : 0;
@@ -166,22 +179,16 @@ __device__ void stage_body(const StageParams& p) {
             s_total[0] = incl;
         }
     } else if (warp == 1) {
-        // per local expert: sum over sources, round up to the alignment, exclusive scan in waves of 32
+        // Phase 2: exclusive scan of the padded sizes in waves of 32 (shared memory only)
         int carry = 0;
         for (int base = 0; base < Le; base += 32) {
             const int l = base + lane;
-            int cnt = 0;
-            if (l < Le)
-                for (int s = 0; s < R; ++s) cnt += ld_relaxed_sys(in + s * msg + 2 + l);
-            const int padded = (cnt + p.alignment - 1) / p.alignment * p.alignment;
+            const int padded = l < Le ? s_padded[l] : 0;
             const int incl = warp_inclusive_sum(padded);
             if (l < Le) {
                 const int off = carry + incl - padded;
-                p.expert_counts[l] = cnt;
                 p.expert_offsets[l] = off;
-                ctrl[L.ctrl_expert_counts() + l] = cnt;
                 ctrl[L.ctrl_expert_offsets() + l] = off;
-                ctrl[L.ctrl_expert_cursor() + l] = 0;
             }
             carry += __shfl_sync(kFull, incl, 31);
         }
@@ -397,16 +404,28 @@ __device__ void pull_body(const PullParams& p) {
                 src = p.c.rank;
                 tok = 0;
             }
-            const char* from = window(p.c, src) + L.stage_rows_offset + int64_t(p.parity) * L.stage_rows_stride + int64_t(tok) * rb;
-            mbar_expect_tx(ring.bar(i), uint32_t(rb));
-            bulk_load(ring.slot(i), from, uint32_t(rb), ring.bar(i));
+            if (src == p.c.rank && p.x_local != nullptr) {
+                mbar_expect_tx(ring.bar(i), uint32_t(H) * 2u);
+                bulk_load(ring.slot(i), p.x_local + int64_t(tok) * H, uint32_t(H) * 2u, ring.bar(i));
+            } else {
+                const char* from = window(p.c, src) + L.stage_rows_offset + int64_t(p.parity) * L.stage_rows_stride + int64_t(tok) * rb;
+                mbar_expect_tx(ring.bar(i), uint32_t(rb));
+                bulk_load(ring.slot(i), from, uint32_t(rb), ring.bar(i));
+            }
         }
     };
     for (int i = 0; i < min(S - 1, n_my); ++i) issue(i);
 
-    // Gaps between an expert's last real row and the next expert's first slot.
+    // Gaps between an expert's last real row and the next expert's first slot: zero rows are bulk
+    // stores from a small zero buffer behind the rings (few instructions, no LSU store traffic).
+    char* zero_buf = s_ring + (align_up(rb, 128) + 8) * int64_t(wpb) * S;
+    zero_buf = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(zero_buf) + 127) & ~uintptr_t(127));
+    if (p.expand && p.zero_padding) {
+        for (int i = threadIdx.x; i < kZeroBytes / 16; i += blockDim.x) reinterpret_cast<int4*>(zero_buf)[i] = make_int4(0, 0, 0, 0);
+        fence_proxy_async_smem();
+        __syncthreads();
+    }
     if (p.expand) {
-        const int vecs = H / 8;
         int base = 0;
         for (int l = 0; l < Le; ++l) {
             const int gs = int(p.expert_offsets[l] + p.expert_counts[l]);
@@ -416,12 +435,17 @@ __device__ void pull_body(const PullParams& p) {
             for (int j = first; j < len; j += GW) {
                 const int64_t row = gs + j;
                 if (p.zero_padding) {
-                    int4* dst = reinterpret_cast<int4*>(p.x_out + row * H);
-                    for (int i = lane; i < vecs; i += 32) dst[i] = make_int4(0, 0, 0, 0);
-                    if (lane == 0 && p.w_out != nullptr) p.w_out[row] = 0.f;
+                    if (lane == 0) {
+                        char* dst = reinterpret_cast<char*>(p.x_out + row * H);
+                        for (int at = 0; at < H * 2; at += kZeroBytes) bulk_store(dst + at, zero_buf, uint32_t(min(kZeroBytes, H * 2 - at)));
+                        bulk_commit();
+                        if (p.w_out != nullptr) p.w_out[row] = 0.f;
+                    }
+                    if (p.tile_ready != nullptr) bulk_wait<0>();
                 }
                 if (lane == 0 && p.slot_map != nullptr) p.slot_map[row] = -1;
                 if (p.tile_ready != nullptr) {
+                    fence_proxy_async();
                     __threadfence();
                     __syncwarp();
                     if (lane == 0) red_release_gpu_add(p.tile_ready + int(row / 128), 1);
@@ -464,6 +488,7 @@ __device__ void pull_body(const PullParams& p) {
         const int v = lane < K ? m[2 + lane] : -1;
         const char* st = ring.slot(i);
         const float* st_w = reinterpret_cast<const float*>(st + wire_weights_offset(H));
+        if (m[0] == p.c.rank && p.x_local != nullptr && p.w_local != nullptr) st_w = p.w_local + int64_t(m[1]) * K;
         if (p.expand) {
             if (v >= 0) {
                 bulk_store(p.x_out + int64_t(v) * H, st, uint32_t(H) * 2u);
@@ -738,6 +763,96 @@ __device__ void reduce_body(const ReduceParams& p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// local combine (single-rank group): sum a row's expert outputs into its source token.
+// ------------------------------------------------------------------------------------------
+__device__ void local_combine_body(const LocalCombineParams& p) {
+    const WindowLayout& L = p.c.layout;
+    const int K = L.topk, H = L.hidden;
+    const int E = int(L.num_experts);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    const int MW = K + 2, vecs = H / 8;
+    const StatusRef status = status_of(p.c);
+    for (int r = gw; r < p.rows; r += GW) {
+        const int* m = p.meta + int64_t(r) * MW;
+        const int tok = m[1];
+        if (m[0] != p.c.rank || tok < 0 || tok >= p.tokens) {
+            if (lane == 0) report(status, kBadMetadata, uint32_t(r), kTagReduce);
+            continue;
+        }
+        const int v = lane < K ? m[2 + lane] : -1;
+        const unsigned vm = __ballot_sync(kFull, p.expand ? (v >= 0 && v < p.capacity) : v >= 0);
+        if (vm == 0) continue;
+        const int4* bias = p.bias != nullptr ? reinterpret_cast<const int4*>(p.bias + int64_t(tok) * H) : nullptr;
+        int4* out = reinterpret_cast<int4*>(p.out + int64_t(tok) * H);
+        for (int c = lane; c < vecs; c += 64) {
+            const bool two = c + 32 < vecs;
+            float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (p.expand) {
+                unsigned left = vm;
+                while (left) {
+                    int k[4];
+                    int4 d0[4], d1[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        k[j] = left ? __ffs(left) - 1 : -1;
+                        if (left) left &= left - 1;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int slot = __shfl_sync(kFull, v, k[j] < 0 ? 0 : k[j]);
+                        if (k[j] >= 0) {
+                            const int4* src = reinterpret_cast<const int4*>(p.y + int64_t(slot) * H);
+                            d0[j] = ld_nc_v4(src + c);
+                            if (two) d1[j] = ld_nc_v4(src + c + 32);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (k[j] >= 0) {
+                            accumulate8(a0, d0[j]);
+                            if (two) accumulate8(a1, d1[j]);
+                        }
+                    }
+                }
+                if (p.round_partial) {
+                    const int4 r0 = pack8(a0), r1 = pack8(a1);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a0[j] = a1[j] = 0.f;
+                    accumulate8(a0, r0);
+                    accumulate8(a1, r1);
+                }
+            } else {
+                const int4* src = reinterpret_cast<const int4*>(p.y + int64_t(r) * H);
+                accumulate8(a0, ld_nc_v4(src + c));
+                if (two) accumulate8(a1, ld_nc_v4(src + c + 32));
+            }
+            if (bias != nullptr) {
+                accumulate8(a0, ld_nc_v4(bias + c));
+                if (two) accumulate8(a1, ld_nc_v4(bias + c + 32));
+            }
+            out[c] = pack8(a0);
+            if (two) out[c + 32] = pack8(a1);
+        }
+        if (p.w_out != nullptr && lane < K) {
+            float wv = 0.f;
+            if ((vm >> lane) & 1u) wv = p.expand ? p.w[v] : p.w[int64_t(r) * K + lane];
+            p.w_out[int64_t(tok) * K + lane] = wv;
+        }
+    }
+    // tokens without any valid choice have no receive row: result = bias (or zero), weights = 0
+    for (int t = gw; t < p.tokens; t += GW) {
+        const int64_t e = lane < K ? p.topk[int64_t(t) * K + lane] : -1;
+        if (__ballot_sync(kFull, e >= 0 && e < E) != 0) continue;
+        int4* out = reinterpret_cast<int4*>(p.out + int64_t(t) * H);
+        const int4* bias = p.bias != nullptr ? reinterpret_cast<const int4*>(p.bias + int64_t(t) * H) : nullptr;
+        for (int c = lane; c < vecs; c += 32) out[c] = bias != nullptr ? ld_nc_v4(bias + c) : make_int4(0, 0, 0, 0);
+        if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = 0.f;
+    }
+}
+
 __device__ void barrier_body(const BarrierParams& p) {
     peer_barrier_warp(p.c.peers, p.c.rank, p.c.layout.ranks, p.c.layout.signal_offset, p.epoch, p.c.timeout_ns, status_of(p.c),
                       kTagBarrier);
@@ -754,6 +869,7 @@ NEP_KERNEL_PAIR(pull, PullParams, 256)
 NEP_KERNEL_PAIR(push, PushParams, 256)
 NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
 NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
+NEP_KERNEL_PAIR(local_combine, LocalCombineParams, kReduceThreads)
 
 template <typename Params>
 cudaError_t launch_pair(void (*single)(const Params), void (*multi)(const Params*), const Params* params, LaunchShape shape, int threads,
@@ -777,20 +893,21 @@ int stage_smem_bytes(const WindowLayout& l) { return int((l.ranks + l.num_expert
 int plan_smem_bytes(const WindowLayout& l) { return (kPlanThreads / 32) * 32 * l.topk * 4; }
 
 RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes) {
+    // smem = warps * stages * (row pitch + one mbarrier) + zero buffer + alignment slack + static smem.
+    // The software pipeline needs at least two stages; a row that does not fit twice is rejected by
+    // the caller (warps == 0).
     const int64_t pitch = align_up(row_bytes, 128);
+    const int64_t fixed = kZeroBytes + 256 + 256;
     RingPlan r{};
-    // The software pipeline needs at least two stages; a row that does not fit twice is rejected
-    // by the caller (warps == 0).
     r.stages = 3;
-    int64_t budget = int64_t(max_smem_bytes) - 1024;
-    int warps = int(budget / (pitch * r.stages + 8 * r.stages));
+    int warps = int((int64_t(max_smem_bytes) - fixed) / ((pitch + 8) * r.stages));
     if (warps < 1) {
         r.stages = 2;
-        warps = int(budget / (pitch * r.stages + 8 * r.stages));
+        warps = int((int64_t(max_smem_bytes) - fixed) / ((pitch + 8) * r.stages));
     }
     if (warps < 1) warps = 0;
     r.warps = warps > 8 ? 8 : warps;
-    r.smem_bytes = size_t(r.warps) * r.stages * (pitch + 8) + 128;
+    r.smem_bytes = size_t(r.warps) * r.stages * (pitch + 8) + kZeroBytes + 256;
     return r;
 }
 
@@ -813,6 +930,10 @@ cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaS
     return launch_pair<BarrierParams>(barrier_kernel, barrier_multi_kernel, params, shape, 32, 0, stream);
 }
 
+cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream) {
+    return launch_pair<LocalCombineParams>(local_combine_kernel, local_combine_multi_kernel, params, shape, kReduceThreads, 0, stream);
+}
+
 int kernel_table(KernelInfo* out, int capacity) {
     struct Entry {
         const char* name;
@@ -821,6 +942,7 @@ int kernel_table(KernelInfo* out, int capacity) {
     const Entry entries[] = {
         {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
         {"push", (const void*)push_kernel},     {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
+        {"local_combine", (const void*)local_combine_kernel},
     };
     int n = 0;
     for (const Entry& e : entries) {

@@ -38,6 +38,7 @@ struct StageParams {
     int fresh;
     int parity;
     int alignment;
+    int skip_copy;  // single-rank groups: the pull reads x directly, nothing is staged
     uint64_t epoch;
     // handle tensors written by a fresh dispatch
     int64_t* snapshot;          // [T,K] copy of topk
@@ -72,6 +73,9 @@ struct PullParams {
     const int64_t* expert_counts;
     const int64_t* expert_offsets;
     const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
+    // Rows whose source is this rank may be read from the caller's tensors instead of the staged copy.
+    const __nv_bfloat16* x_local;  // [T,H] or null
+    const float* w_local;          // [T,K] or null
     int* tile_ready;  // optional: [C/128] counters, +1 per expert-major row (data or zero padding) once it is in memory
 };
 
@@ -103,6 +107,22 @@ struct ReduceParams {
     int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank (first k)
 };
 
+// Single-rank combine: every contribution is local, so the expert outputs are summed straight into
+// the result (same FP32 order and rounding points as push + reduce).
+struct LocalCombineParams {
+    CommonParams c;
+    const __nv_bfloat16* y;      // [N,H] or [C,H]
+    const float* w;              // receive-layout weights or null
+    const int* meta;             // [N,K+2]
+    const int64_t* topk;         // [T,K] source routing snapshot
+    const __nv_bfloat16* bias;   // [T,H] or null
+    __nv_bfloat16* out;          // [T,H]
+    float* w_out;                // [T,K] or null
+    int rows, capacity, tokens;
+    int expand;
+    int round_partial;  // expanded + multiple reduction: bf16 round of the local sum before bias
+};
+
 struct BarrierParams {
     CommonParams c;
     uint64_t epoch;
@@ -121,6 +141,7 @@ cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, 
 cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
 cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream);
 cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaStream_t stream);
+cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream);
 
 // Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.
 struct RingPlan {

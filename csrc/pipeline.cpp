@@ -242,6 +242,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.fresh = fresh;
             p.parity = parity[i];
             p.alignment = int(alignment);
+            p.skip_copy = L.ranks == 1 ? 1 : 0;
             p.epoch = wins[i]->reserve_epochs(1);
             if (fresh) {
                 p.snapshot = m[5].data_ptr<int64_t>();
@@ -321,6 +322,8 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.expert_counts = m[1].data_ptr<int64_t>();
             p.expert_offsets = m[2].data_ptr<int64_t>();
             p.recv_rank_prefix = m[6].data_ptr<int64_t>();
+            p.x_local = reinterpret_cast<const __nv_bfloat16*>(xs[i].data_ptr());
+            p.w_local = weighted ? weights[i]->data_ptr<float>() : nullptr;
             if (int(tile_ready.size()) == n && tile_ready[i].has_value()) {
                 const auto& t = *tile_ready[i];
                 TORCH_CHECK(expand && zero_padding, "tile counters need the expert-major layout with zero padding");
@@ -404,6 +407,46 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
 
     CombineOut out;
     out.outputs.resize(n);
+    if (L.ranks == 1) {
+        // Everything is local: one kernel sums the expert outputs straight into the result.
+        LocalCombineParams p{};
+        {
+            c10::cuda::CUDAStreamGuard pool(consumer);
+            const auto& m = meta[0];
+            const int64_t T = m[5].size(0);
+            auto& o = out.outputs[0];
+            o.resize(2);
+            o[0] = at::empty({T, L.hidden}, bf16);
+            o[1] = weighted ? at::empty({T, L.topk}, f32) : at::empty({0}, f32);
+            p.c = wins[0]->common();
+            p.y = reinterpret_cast<const __nv_bfloat16*>(xs[0].data_ptr());
+            p.w = weighted ? weights[0]->data_ptr<float>() : nullptr;
+            p.meta = m[0].data_ptr<int>();
+            p.topk = m[5].data_ptr<int64_t>();
+            p.bias = bias[0].has_value() ? reinterpret_cast<const __nv_bfloat16*>(bias[0]->data_ptr()) : nullptr;
+            p.out = reinterpret_cast<__nv_bfloat16*>(o[0].data_ptr());
+            p.w_out = weighted ? o[1].data_ptr<float>() : nullptr;
+            p.rows = int(m[0].size(0));
+            p.capacity = int(capacity[0]);
+            p.tokens = int(T);
+            p.expand = expand;
+            p.round_partial = (expand && allow_multiple_reduction) ? 1 : 0;
+        }
+        {
+            c10::cuda::CUDAStreamGuard on_comm(s.comm);
+            g_marks.mark("begin", cs);
+            PeerWindow::launches += 1;
+            cuda_check(launch_local_combine(&p, LaunchShape{2 * lim.sms, 1}, cs), "local combine launch");
+            g_marks.mark("local_combine", cs);
+        }
+        std::vector<at::Tensor> inputs{xs[0]}, results;
+        if (weighted) inputs.push_back(*weights[0]);
+        if (bias[0].has_value()) inputs.push_back(*bias[0]);
+        for (auto& t : meta[0]) inputs.push_back(t);
+        for (auto& t : out.outputs[0]) results.push_back(t);
+        out.event = finish(s, async_op, std::move(inputs), std::move(results));
+        return out;
+    }
     std::vector<PushParams> push(n);
     std::vector<ReduceParams> reduce(n);
     std::vector<at::Tensor> keep;
