@@ -87,7 +87,9 @@ def gemm_only(args, device):
     out = {}
     for name, fn, flops in (
         ("up_swiglu", lambda: gg.grouped_gemm(a, w13, offsets, swiglu=True), 2.0 * rows * args.hidden * 2 * args.inter),
+        ("up_swiglu_3stage", lambda: gg.grouped_gemm(a, w13, offsets, swiglu=True, stages=3), 2.0 * rows * args.hidden * 2 * args.inter),
         ("down", lambda: gg.grouped_gemm(h, w2, offsets), 2.0 * rows * args.hidden * args.inter),
+        ("down_3stage", lambda: gg.grouped_gemm(h, w2, offsets, stages=3), 2.0 * rows * args.hidden * args.inter),
         ("cublas_up", lambda: torch.bmm(a.view(local, rows_per, args.hidden), w13.transpose(1, 2)), 2.0 * rows * args.hidden * 2 * args.inter),
         ("cublas_down", lambda: torch.bmm(h.view(local, rows_per, args.inter), w2.transpose(1, 2)), 2.0 * rows * args.hidden * args.inter),
     ):
@@ -145,10 +147,12 @@ def run(args):
         results = []
         with CudaBuffer(control, EPConfig(E, K, H, T)) as buf:
             layers = {
-                "fused": ExpertParallelMoE(buf, w13, w2, fuse_combine=True, overlap_dispatch=True, comm_sms=args.comm_sms),
+                "fused": ExpertParallelMoE(buf, w13, w2, fuse_combine=True, overlap_dispatch=True),
                 "fused_combine": ExpertParallelMoE(buf, w13, w2, fuse_combine=True, overlap_dispatch=False),
+                "fused_serialized": ExpertParallelMoE(buf, w13, w2, fuse_combine=True, overlap_dispatch=True),
                 "unfused": ExpertParallelMoE(buf, w13, w2, fuse_combine=False, overlap_dispatch=False),
             }
+            layers["fused_serialized"].serialize_overlap = True
             probe = layers["unfused"]
             probe(x, idx, w)
             torch.cuda.synchronize()
@@ -168,6 +172,11 @@ def run(args):
                 ms = reduce_max(statistics.median(timed(lambda: layer(x, idx, w), args.steps, args.warmup, flush)))
                 buf.check_status()
                 gg.check_status()
+                layer.profile = True
+                layer(x, idx, w)
+                layer(x, idx, w)
+                layer.profile = False
+                profile = {k: reduce_max(v) for k, v in layer.last_profile.items()}
                 t_compute = reduce_max(flops / (burst * 1e12)) * 1e3
                 t_link = reduce_max(nvlink_bytes / (PEER_GBS * 1e9)) * 1e3 if world > 1 else 0.0
                 results.append({
@@ -177,6 +186,7 @@ def run(args):
                     "roofline_ms": max(t_compute, t_link), "roofline_frac": max(t_compute, t_link) / ms,
                     "roofline_terms_ms": {"compute_at_burst_peak": t_compute, "nvlink_at_770GBs": t_link}, "peak_basis": basis,
                     "rows": {"valid": rows_valid, "padded": rows_padded, "recv_dedup": n_recv},
+                    "steps_us": profile,
                 })
         if "nccl" in args.arms.split(","):
             nccl = dist.group.WORLD

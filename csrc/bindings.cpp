@@ -25,6 +25,7 @@ py::dict layout_dict(const nep::WindowLayout& w) {
     d["ret_offset"] = w.ret_offset;
     d["ret_stride"] = w.ret_stride;
     d["meta_scratch_offset"] = w.meta_scratch_offset;
+    d["slot_scratch_offset"] = w.slot_scratch_offset;
     d["num_bytes"] = w.num_bytes;
     d["row_bytes"] = w.row_bytes();
     d["msg_ints"] = w.msg_ints();
@@ -88,15 +89,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            const std::vector<c10::optional<at::Tensor>>& weights, const std::vector<std::vector<at::Tensor>>& cached_meta,
            const std::vector<int64_t>& cached_capacity, int64_t alignment, bool expand, bool zero_padding, int64_t num_sms,
            int64_t comm_stream, int64_t previous_event, bool async_op, double mailbox_timeout_s,
-           const std::vector<c10::optional<at::Tensor>>& tile_ready) {
+           const std::vector<c10::optional<at::Tensor>>& tile_ready, int64_t ring_smem_limit) {
             auto out = nep::dispatch(wins, xs, topks, weights, cached_meta, cached_capacity, alignment, expand, zero_padding, num_sms,
-                                     comm_stream, previous_event, async_op, mailbox_timeout_s, tile_ready);
+                                     comm_stream, previous_event, async_op, mailbox_timeout_s, tile_ready, ring_smem_limit);
             return py::make_tuple(out.outputs, out.metadata, out.counts, out.event);
         },
         py::arg("windows"), py::arg("x"), py::arg("topk_idx"), py::arg("weights"), py::arg("cached_metadata"), py::arg("cached_capacity"),
         py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("num_sms"), py::arg("comm_stream"),
         py::arg("previous_event"), py::arg("async_op"), py::arg("mailbox_timeout_s") = 60.0,
-        py::arg("tile_ready") = std::vector<c10::optional<at::Tensor>>{});
+        py::arg("tile_ready") = std::vector<c10::optional<at::Tensor>>{}, py::arg("ring_smem_limit") = 0);
 
     m.def(
         "combine",

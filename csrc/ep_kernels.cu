@@ -229,6 +229,14 @@ __device__ void plan_body(const PlanParams& p) {
     const StatusRef status = status_of(p.c);
     const int cps = int((L.max_tokens + 31) / 32);
     const int lo = p.c.rank * Le;
+    int* slot_scratch = reinterpret_cast<int*>(window(p.c, p.c.rank) + L.slot_scratch_offset);
+    if (p.expand) {
+        // alignment gaps of the expert-major layout hold no row
+        const int* ecnt = ctrl + L.ctrl_expert_counts();
+        for (int l = gw; l < Le; l += GW)
+            for (int slot = eoff[l] + ecnt[l] + lane; slot < eoff[l + 1]; slot += 32)
+                if (slot < L.slot_scratch_ints) slot_scratch[slot] = -1;
+    }
 
     for (int c = gw; c < R * cps; c += GW) {
         const int s = c / cps, tok0 = (c % cps) * 32;
@@ -292,6 +300,7 @@ __device__ void plan_body(const PlanParams& p) {
                                 report(status, kSlotOverflow, uint32_t(v), kTagPlan);
                                 v = -1;
                             }
+                            if (p.expand && v >= 0 && v < L.slot_scratch_ints) slot_scratch[v] = row * K + k0 + j;
                         }
                         m[2 + k0 + j] = v;
                     }
@@ -392,11 +401,24 @@ __device__ void pull_body(const PullParams& p) {
     Ring ring = make_ring(s_ring, wpb, p.stages, rb);
     const int S = p.stages;
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
-    const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
+    const bool slot_order = p.slot_src != nullptr;
+    const int n_items = slot_order ? p.capacity : walk.items;
+    const int n_my = n_items > gw ? (n_items - gw + GW - 1) / GW : 0;
+    // item -> receive row to transfer now (false: nothing to do for this item)
+    auto locate = [&](int item, int& r) {
+        if (!slot_order) return walk.locate(item, r);
+        const int a = p.slot_src[item];
+        r = a >= 0 ? a / K : 0;
+        const int v = (a >= 0 && lane < K) ? p.meta[int64_t(r) * MW + 2 + lane] : -1;
+        int lowest = v >= 0 ? v : 0x7fffffff;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) lowest = min(lowest, __shfl_xor_sync(kFull, lowest, d));
+        return a >= 0 && lowest == item;
+    };
 
     auto issue = [&](int i) {
         int r;
-        const bool live = walk.locate(gw + i * GW, r);
+        const bool live = locate(gw + i * GW, r);
         if (lane == 0 && live) {
             int src = p.meta[int64_t(r) * MW], tok = p.meta[int64_t(r) * MW + 1];
             if (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens) {
@@ -472,7 +494,7 @@ __device__ void pull_body(const PullParams& p) {
     };
     for (int i = 0; i < n_my; ++i) {
         int r;
-        if (!walk.locate(gw + i * GW, r)) {
+        if (!locate(gw + i * GW, r)) {
             bulk_commit();
             retire_previous();
             announced_slot = -1;
@@ -901,9 +923,12 @@ RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes) {
     RingPlan r{};
     r.stages = 3;
     int warps = int((int64_t(max_smem_bytes) - fixed) / ((pitch + 8) * r.stages));
-    if (warps < 1) {
+    // Under a small budget two warps with two stages beat one warp with three: the same number of
+    // loads in flight, twice the instruction issue.
+    const int warps2 = int((int64_t(max_smem_bytes) - fixed) / ((pitch + 8) * 2));
+    if (warps < 2 && warps2 > warps) {
         r.stages = 2;
-        warps = int((int64_t(max_smem_bytes) - fixed) / ((pitch + 8) * r.stages));
+        warps = warps2;
     }
     if (warps < 1) warps = 0;
     r.warps = warps > 8 ? 8 : warps;

@@ -73,6 +73,10 @@ struct PullParams {
     const int64_t* expert_counts;
     const int64_t* expert_offsets;
     const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
+    // Slot-ordered walk (expert-major layout): items are the output slots in ascending order and a
+    // row is transferred when its lowest slot comes up, so row blocks fill front to back.
+    const int* slot_src;  // [C] slot -> row*K+k (-1 = gap) or null for the row-ordered walk
+    int capacity;
     // Rows whose source is this rank may be read from the caller's tensors instead of the staged copy.
     const __nv_bfloat16* x_local;  // [T,H] or null
     const float* w_local;          // [T,K] or null

@@ -94,7 +94,8 @@ void bind_gemm(pybind11::module_& m) {
     m.def(
         "grouped_gemm",
         [](const at::Tensor& a, const at::Tensor& w, const at::Tensor& expert_offsets, at::Tensor& out, at::Tensor& status, int64_t mode,
-           c10::optional<at::Tensor> tile_ready, c10::optional<at::Tensor> tile_expected, int64_t max_ctas, double timeout_s) {
+           c10::optional<at::Tensor> tile_ready, c10::optional<at::Tensor> tile_expected, int64_t max_ctas, double timeout_s,
+           c10::optional<at::Tensor> row_scale, int64_t stages) {
             c10::cuda::CUDAGuard guard(a.device());
             TORCH_CHECK(mode == gemm::kPlain || mode == gemm::kSwiGLU, "mode must be 0 (plain) or 1 (SwiGLU)");
             auto g = prepare(a, w, expert_offsets, status, int(mode), timeout_s);
@@ -110,15 +111,23 @@ void bind_gemm(pybind11::module_& m) {
                 g.args.tile_ready = tile_ready->data_ptr<int>();
                 g.args.tile_expected = tile_expected->data_ptr<int>();
             }
+            if (row_scale.has_value()) {
+                TORCH_CHECK(mode == gemm::kPlain && row_scale->is_cuda() && row_scale->scalar_type() == at::kFloat &&
+                                row_scale->is_contiguous() && row_scale->numel() == a.size(0),
+                            "row_scale must be float32 [rows] (plain mode only)");
+                g.args.row_scale = row_scale->data_ptr<float>();
+            }
+            TORCH_CHECK(stages == 3 || stages == 4, "stages must be 3 or 4");
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;
             PeerWindow::launches += 1;
-            cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, int(mode), grid, c10::cuda::getCurrentCUDAStream().stream());
+            cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, int(mode), int(stages), grid, c10::cuda::getCurrentCUDAStream().stream());
             TORCH_CHECK(e == cudaSuccess, "grouped GEMM launch failed: ", cudaGetErrorString(e));
         },
         pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"), pybind11::arg("out"), pybind11::arg("status"),
         pybind11::arg("mode"), pybind11::arg("tile_ready") = c10::nullopt, pybind11::arg("tile_expected") = c10::nullopt,
-        pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0);
+        pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0, pybind11::arg("row_scale") = c10::nullopt,
+        pybind11::arg("stages") = 4);
 
     // Down projection fused with the combine push: row r of (A @ W[e]^T) * slot_weight[r] is stored
     // (bf16) into the return partition of the row's source rank; padding rows are skipped.
@@ -151,7 +160,7 @@ void bind_gemm(pybind11::module_& m) {
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;
             PeerWindow::launches += 1;
-            cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, gemm::kScatter, grid, c10::cuda::getCurrentCUDAStream().stream());
+            cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, gemm::kScatter, 3, grid, c10::cuda::getCurrentCUDAStream().stream());
             TORCH_CHECK(e == cudaSuccess, "grouped GEMM (scatter) launch failed: ", cudaGetErrorString(e));
         },
         pybind11::arg("window"), pybind11::arg("parity"), pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"),
@@ -159,7 +168,7 @@ void bind_gemm(pybind11::module_& m) {
         pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0);
 
     m.def("gemm_kernel_registers", [](int64_t mode) { return gemm::kernel_registers(int(mode)); });
-    m.def("gemm_shared_bytes", [] { return int64_t(gemm::shared_bytes()); });
+    m.def("gemm_shared_bytes", [](int64_t mode, int64_t stages) { return int64_t(gemm::shared_bytes(int(mode), int(stages))); });
 }
 
 }  // namespace nep

@@ -32,13 +32,17 @@ namespace gemm {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;  // 16 KB
 constexpr int kBBytes = BN * BK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kMaxExperts = 1024;
+// kScatter stages its 128 x 256 bf16 output tile in shared memory (one 512-byte row per thread,
+// padded to 528 bytes against bank conflicts) and sends each row with one bulk store.
+constexpr int kOutRowBytes = BN * 2;
+constexpr int kOutPitch = kOutRowBytes + 16;
+constexpr int kOutStageBytes = 4 * 32 * kOutPitch;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint64_t timer_ns() {
@@ -137,8 +141,9 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     return v;
 }
 
+constexpr int kMaxStages = 4;
 struct SharedStorage {
-    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort;
     int offsets[kMaxExperts + 1];
@@ -153,12 +158,20 @@ __device__ __forceinline__ int find_expert(const int* offsets, int experts, int 
     return lo;
 }
 
-template <int kMode>
+__device__ __forceinline__ void bulk_store_row(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int kMode, int kStages>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                    const __grid_constant__ CUtensorMap map_b, const Args args) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* tiles = smem;  // kStages x (A 16 KB | B 32 KB), 1024-byte aligned
     SharedStorage& sh = *reinterpret_cast<SharedStorage*>(smem + kStages * kStageBytes);
+    uint8_t* out_stage = smem + kStages * kStageBytes + ((sizeof(SharedStorage) + 127) / 128) * 128;  // kScatter only
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint64_t limit_ns = args.timeout_ns;
 
@@ -314,44 +327,62 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
                     st_v4(out_row + c, o[0], o[1], o[2], o[3]);
                     st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
                 }
-            } else {
-                // kPlain writes the local output; kScatter scales by the slot's gate weight and writes
-                // into the source rank's return partition (a peer pointer) or skips padding rows.
-                __nv_bfloat16* out_row = nullptr;
-                float scale = 1.f;
-                if (kMode == kPlain) {
-                    out_row = args.out + int64_t(row) * args.ldo + nt * BN;
-                } else {
-                    const int a = args.slot_map[row];
-                    if (a >= 0) {
-                        const int recv_row = a / args.topk, k = a % args.topk;
-                        const int* meta = args.recv_metadata + int64_t(recv_row) * (args.topk + 2);
-                        const int src = meta[0], tok = meta[1];
-                        scale = args.slot_weights != nullptr ? args.slot_weights[row] : 1.f;
-                        out_row = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(args.peers[src]) + args.ret_offset +
-                                                                   (int64_t(k) * args.max_tokens + tok) * int64_t(args.ldo) * 2) +
-                                  nt * BN;
-                    }
-                }
+            } else if (kMode == kPlain) {
+                __nv_bfloat16* out_row = args.out + int64_t(row) * args.ldo + nt * BN;
+                const float scale = args.row_scale != nullptr ? args.row_scale[row] : 1.f;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c, v);
                     tmem_ld_wait();
-                    if (out_row != nullptr) {
-                        uint32_t o[8];
+                    uint32_t o[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
-                        st_v4(out_row + c, o[0], o[1], o[2], o[3]);
-                        st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
-                    }
+                    for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
+                    st_v4(out_row + c, o[0], o[1], o[2], o[3]);
+                    st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
                 }
+            } else {
+                // kScatter: acc * gate weight -> bf16 row in shared memory -> one 512-byte bulk store into
+                // the source rank's return partition (peer memory over NVLink, or local).  Padding rows
+                // are skipped.
+                __nv_bfloat16* out_row = nullptr;
+                float scale = 1.f;
+                const int a = args.slot_map[row];
+                if (a >= 0) {
+                    const int recv_row = a / args.topk, k = a % args.topk;
+                    const int* meta = args.recv_metadata + int64_t(recv_row) * (args.topk + 2);
+                    const int src = meta[0], tok = meta[1];
+                    scale = args.slot_weights != nullptr ? args.slot_weights[row] : 1.f;
+                    out_row = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(args.peers[src]) + args.ret_offset +
+                                                               (int64_t(k) * args.max_tokens + tok) * int64_t(args.ldo) * 2) +
+                              nt * BN;
+                }
+                uint8_t* my_row = out_stage + (quarter * 32 + lane) * kOutPitch;
+                // the previous tile's bulk store must have finished reading this row buffer
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c, v);
+                    tmem_ld_wait();
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
+                    st_shared_v4(my_row + c * 2, o[0], o[1], o[2], o[3]);
+                    st_shared_v4(my_row + c * 2 + 16, o[4], o[5], o[6], o[7]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (out_row != nullptr) bulk_store_row(out_row, my_row, kOutRowBytes);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.tmem_empty[acc]);
         }
-        if (kMode == kScatter) __threadfence_system();
+        if (kMode == kScatter) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __threadfence_system();
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -363,33 +394,36 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
 
 }  // namespace
 
-size_t shared_bytes() { return size_t(kStages) * kStageBytes + sizeof(SharedStorage) + 1024; }
+size_t shared_bytes(int mode, int stages) {
+    return size_t(stages) * kStageBytes + ((sizeof(SharedStorage) + 127) / 128) * 128 + (mode == kScatter ? kOutStageBytes : 0) + 128;
+}
 
-template <int kMode>
+template <int kMode, int kStages>
 cudaError_t launch_mode(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int grid, cudaStream_t stream) {
-    auto* fn = grouped_gemm_kernel<kMode>;
-    const size_t smem = shared_bytes();
+    auto* fn = grouped_gemm_kernel<kMode, kStages>;
+    const size_t smem = shared_bytes(kMode, kStages);
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
     fn<<<grid, kThreads, smem, stream>>>(a, b, args);
     return cudaGetLastError();
 }
 
-cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream) {
+// `stages` = 4 by default; 3 leaves ~75 KB of shared memory per SM for a co-resident transfer kernel.
+cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int stages, int grid, cudaStream_t stream) {
     if (args.num_experts > kMaxExperts) return cudaErrorInvalidValue;
-    switch (mode) {
-        case kPlain: return launch_mode<kPlain>(a, b, args, grid, stream);
-        case kSwiGLU: return launch_mode<kSwiGLU>(a, b, args, grid, stream);
-        case kScatter: return launch_mode<kScatter>(a, b, args, grid, stream);
-        default: return cudaErrorInvalidValue;
-    }
+    if (mode == kPlain && stages == 4) return launch_mode<kPlain, 4>(a, b, args, grid, stream);
+    if (mode == kPlain && stages == 3) return launch_mode<kPlain, 3>(a, b, args, grid, stream);
+    if (mode == kSwiGLU && stages == 4) return launch_mode<kSwiGLU, 4>(a, b, args, grid, stream);
+    if (mode == kSwiGLU && stages == 3) return launch_mode<kSwiGLU, 3>(a, b, args, grid, stream);
+    if (mode == kScatter) return launch_mode<kScatter, 3>(a, b, args, grid, stream);
+    return cudaErrorInvalidValue;
 }
 
 int kernel_registers(int mode) {
     cudaFuncAttributes attr{};
-    const void* fn = mode == kPlain ? (const void*)grouped_gemm_kernel<kPlain>
-                   : mode == kSwiGLU ? (const void*)grouped_gemm_kernel<kSwiGLU>
-                                     : (const void*)grouped_gemm_kernel<kScatter>;
+    const void* fn = mode == kPlain ? (const void*)grouped_gemm_kernel<kPlain, 4>
+                   : mode == kSwiGLU ? (const void*)grouped_gemm_kernel<kSwiGLU, 4>
+                                     : (const void*)grouped_gemm_kernel<kScatter, 3>;
     if (cudaFuncGetAttributes(&attr, fn) != cudaSuccess) {
         cudaGetLastError();
         return -1;

@@ -21,6 +21,7 @@ struct Args {
     int swiglu_up_row_offset;  // I: distance from a gate row to its up row
     __nv_bfloat16* out;      // [rows, ldo] (kPlain / kSwiGLU)
     int ldo;                 // output row length in elements (also the hidden size for kScatter)
+    const float* row_scale;  // kPlain: optional per-row factor applied in FP32 before the bf16 round
     uint32_t* status;        // 2 words: [0] first error code, [1] CTA
     uint64_t timeout_ns;
     // tile gating (optional): row block mb may be loaded once tile_ready[mb] >= tile_expected[mb]
@@ -36,8 +37,8 @@ struct Args {
     int topk;
 };
 
-size_t shared_bytes();
-cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream);
+size_t shared_bytes(int mode, int stages);
+cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int stages, int grid, cudaStream_t stream);
 int kernel_registers(int mode);
 
 }  // namespace gemm

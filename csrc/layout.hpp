@@ -51,6 +51,8 @@ struct WindowLayout {
     int64_t ret_offset;          // [2] bf16[K][Tmax][H] expert outputs pushed back by combine
     int64_t ret_stride;
     int64_t meta_scratch_offset; // i32[R*Tmax][K+2] receive plan of a fresh dispatch (local only)
+    int64_t slot_scratch_offset; // i32[slot_scratch_ints] expert-major slot -> row*K+k of a fresh dispatch (local only)
+    int64_t slot_scratch_ints;
     int64_t num_bytes;
 
     // ctrl sub-layout, in int32 units from ctrl_offset.
@@ -103,6 +105,8 @@ struct WindowLayout {
         w.ret_stride = align_up(int64_t(topk) * max_tokens * hidden * 2, kRegionAlign);
         w.ret_offset = take(2 * w.ret_stride);
         w.meta_scratch_offset = take(int64_t(ranks) * max_tokens * (topk + 2) * 4);
+        w.slot_scratch_ints = int64_t(ranks) * max_tokens * topk + int64_t(w.local_experts) * 128;
+        w.slot_scratch_offset = take(w.slot_scratch_ints * 4);
         w.num_bytes = at;
         return w;
     }

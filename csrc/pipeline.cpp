@@ -169,7 +169,8 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
                      const std::vector<c10::optional<at::Tensor>>& topks, const std::vector<c10::optional<at::Tensor>>& weights,
                      const std::vector<std::vector<at::Tensor>>& cached_meta, const std::vector<int64_t>& cached_capacity,
                      int64_t alignment, bool expand, bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
-                     bool async_op, double mailbox_timeout_s, const std::vector<c10::optional<at::Tensor>>& tile_ready) {
+                     bool async_op, double mailbox_timeout_s, const std::vector<c10::optional<at::Tensor>>& tile_ready,
+                     int64_t ring_smem_limit) {
     validate_group(wins);
     const int n = int(wins.size());
     TORCH_CHECK(int(xs.size()) == n && int(topks.size()) == n && int(weights.size()) == n && int(cached_meta.size()) == n &&
@@ -190,7 +191,9 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     }
     const DeviceLimits lim = device_limits();
     TORCH_CHECK(num_sms >= 1 && num_sms <= lim.sms, "num_sms out of range");
-    const RingPlan ring = plan_ring(L.row_bytes(), lim.smem_optin);
+    // A smaller ring leaves shared memory for a compute kernel that shares the SMs with the pull.
+    const int ring_budget = ring_smem_limit > 0 ? int(std::min<int64_t>(ring_smem_limit, lim.smem_optin)) : lim.smem_optin;
+    const RingPlan ring = plan_ring(L.row_bytes(), ring_budget);
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
     if (fresh) {
         cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
@@ -331,6 +334,12 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
                                 t.numel() * 128 >= C,
                             "tile_ready must be a zeroed CUDA int32 tensor with one entry per 128 expert-major rows");
                 p.tile_ready = t.data_ptr<int>();
+                // Consumers gated by the counters want row blocks to complete front to back.
+                if (!fresh || C <= L.slot_scratch_ints) {
+                    p.slot_src = fresh ? reinterpret_cast<const int*>(static_cast<char*>(wins[i]->base()) + L.slot_scratch_offset)
+                                       : m[7].data_ptr<int>();
+                    p.capacity = int(C);
+                }
             }
         }
     }

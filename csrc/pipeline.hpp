@@ -44,7 +44,8 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
                      const std::vector<c10::optional<at::Tensor>>& topks, const std::vector<c10::optional<at::Tensor>>& weights,
                      const std::vector<std::vector<at::Tensor>>& cached_meta, const std::vector<int64_t>& cached_capacity,
                      int64_t alignment, bool expand, bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
-                     bool async_op, double mailbox_timeout_s, const std::vector<c10::optional<at::Tensor>>& tile_ready = {});
+                     bool async_op, double mailbox_timeout_s, const std::vector<c10::optional<at::Tensor>>& tile_ready = {},
+                     int64_t ring_smem_limit = 0);
 
 CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::Tensor>& xs, const std::vector<std::vector<at::Tensor>>& meta,
                    const std::vector<int64_t>& capacity, const std::vector<c10::optional<at::Tensor>>& weights,

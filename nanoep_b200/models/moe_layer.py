@@ -5,13 +5,14 @@
 The reference library leaves the expert computation to the caller (its example uses element-wise
 experts, nano_ep/examples/moe.py:19-40).  This layer is the fused path:
 
-* dispatch runs with the expert-major layout, 128-row alignment and zero padding, on a small SM
-  budget, and announces every finished row in per-block counters;
-* the up/gate grouped GEMM (SwiGLU epilogue) starts at once on the remaining SMs and consumes row
-  blocks as their counters fill, so the NVLink pull hides under tensor-core work;
-* the down-projection GEMM applies the gate weight in FP32 in its epilogue and stores the bf16 rows
-  straight into the source ranks' return partitions over NVLink; a peer barrier and the source-side
-  FP32 reduction finish the combine.
+* dispatch runs with the expert-major layout, 128-row alignment and zero padding, with a small
+  shared-memory ring per SM, and announces every finished row in per-block counters;
+* the up/gate grouped GEMM (SwiGLU epilogue) starts at once on the SAME SMs (its operand pipeline is
+  one stage shorter so both kernels fit in shared memory) and consumes row blocks as their counters
+  fill, so the NVLink pull hides under tensor-core work;
+* the down-projection GEMM applies the gate weight in FP32 in its epilogue, stages each bf16 output
+  row in shared memory and bulk-stores it straight into the source rank's return partition over
+  NVLink; a peer barrier and the source-side FP32 reduction finish the combine.
 
 ``fuse_combine=False`` / ``overlap_dispatch=False`` select the unfused compositions of the same
 public operations (used as correctness and performance baselines).
@@ -29,7 +30,7 @@ ALIGNMENT = 128
 
 class ExpertParallelMoE:
     def __init__(self, buffer: CudaBuffer, w13: torch.Tensor, w2: torch.Tensor, *, fuse_combine: bool = True,
-                 overlap_dispatch: bool = True, comm_sms: int = 32):
+                 overlap_dispatch: bool = True, comm_ring_bytes: int = 72 * 1024):
         cfg = buffer.config
         local = cfg.num_experts // buffer.world_size
         if w13.dim() != 3 or w13.shape[0] != local or w13.shape[2] != cfg.hidden or w13.shape[1] % 256:
@@ -47,43 +48,75 @@ class ExpertParallelMoE:
         self.overlap_dispatch = overlap_dispatch
         self.device = w13.device
         self.device_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.comm_sms = max(1, min(comm_sms, self.device_sms - 8))
+        self.comm_ring_bytes = int(comm_ring_bytes)
         rows_cap = buffer.world_size * cfg.num_max_tokens_per_rank * min(cfg.num_topk, local) + local * (ALIGNMENT - 1)
         blocks = rows_cap // ALIGNMENT + 2
         self._tile_ready = torch.zeros(blocks, dtype=torch.int32, device=self.device)
         self._tile_expected = torch.full((blocks,), ALIGNMENT, dtype=torch.int32, device=self.device)
         self._ext = gg._ext()
+        self.serialize_overlap = False  # diagnostics: run the overlap-mode kernels back to back instead of concurrently
+        self.profile = False  # when set, forward() records CUDA events between its steps (see last_profile)
+        self.last_profile: dict[str, float] = {}
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, *, handle=None, bias=None) -> torch.Tensor:
         buf = self.buffer
         stream = torch.cuda.current_stream(self.device)
         overlap = self.overlap_dispatch
+        marks = []
+
+        def mark(name):
+            if self.profile:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                marks.append((name, ev))
+
+        mark("start")
         if overlap:
             self._tile_ready.zero_()
         got = buf.dispatch(
             x, topk_idx=None if handle is not None else topk_idx, weights=topk_weights, handle=handle,
             do_expand=True if handle is None else None, alignment=ALIGNMENT if handle is None else None, zero_padding=True,
-            async_op=overlap, num_sms=self.comm_sms if overlap else None, tile_ready=self._tile_ready if overlap else None,
+            async_op=overlap, tile_ready=self._tile_ready if overlap else None,
+            ring_smem_limit=self.comm_ring_bytes if overlap else 0,
         )
         h_in, offsets = got.x, got.handle.layout.expert_offsets
         if overlap:
             # The GEMM must not wait for the whole dispatch: it is gated per row block by the counters.
             h_in.record_stream(stream)
+            if self.serialize_overlap:
+                got.event.current_stream_wait()
+                mark("dispatch_small_ring")
             h = gg.grouped_gemm(h_in, self.w13, offsets, swiglu=True, tile_ready=self._tile_ready, tile_expected=self._tile_expected,
-                                max_ctas=self.device_sms - self.comm_sms)
+                                stages=3)
             got.event.current_stream_wait()  # metadata and slot weights are complete from here on
+            mark("dispatch+up_gemm")
         else:
+            mark("dispatch")
             h = gg.grouped_gemm(h_in, self.w13, offsets, swiglu=True)
+            mark("up_gemm")
         self.last_handle = got.handle
         if self.fuse_combine:
             window = buf.window
             parity = self._ext.next_combine_parity(window)
             self._ext.grouped_gemm_scatter(window, parity, h, self.w2, offsets, got.handle.slot_map, got.handle.layout.recv_metadata,
                                            got.topk_weights, gg.status_tensor(self.device), 0, 5.0)
-            return self._ext.combine_finish([window], [handle_metadata(got.handle)], [parity], [bias])[0]
-        y = gg.grouped_gemm(h, self.w2, offsets)
-        y = (y.float() * got.topk_weights[:, None]).to(torch.bfloat16)
-        return buf.combine(y, got.handle, bias=bias).x
+            mark("down_gemm_scatter")
+            out = self._ext.combine_finish([window], [handle_metadata(got.handle)], [parity], [bias])[0]
+            mark("barrier+reduce")
+            self._collect(marks)
+            return out
+        y = gg.grouped_gemm(h, self.w2, offsets, row_scale=got.topk_weights)  # gate weight in FP32 in the epilogue
+        mark("down_gemm")
+        out = buf.combine(y, got.handle, bias=bias).x
+        mark("combine")
+        self._collect(marks)
+        return out
+
+    def _collect(self, marks):
+        if not self.profile or not marks:
+            return
+        marks[-1][1].synchronize()
+        self.last_profile = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) * 1e3 for i in range(1, len(marks))}
 
     __call__ = forward
 

@@ -200,12 +200,15 @@ class CudaBuffer:
         async_op: bool = False,
         num_sms: int | None = None,
         tile_ready: torch.Tensor | None = None,
+        ring_smem_limit: int = 0,
     ) -> NativeDispatchResult:
         """Send every token once to each rank that owns one of its experts; return exact layouts.
 
         ``tile_ready`` (optional, expert-major layout with zero padding only): a zeroed int32 tensor with
         one counter per 128 output rows; the pull kernel adds one per row once the row is in memory,
         so a consumer kernel on another stream can start on a row block as soon as it is complete.
+        ``ring_smem_limit`` caps the pull kernel's shared-memory ring (bytes per CTA) so that such a
+        consumer can share the SMs with it; 0 uses all of the CTA's shared memory.
         """
         check_torch_deterministic()
         if self._closed:
@@ -236,6 +239,7 @@ class CudaBuffer:
                 bool(async_op),
                 self._mailbox_timeout_s,
                 [tile_ready],
+                int(ring_smem_limit),
             )
         if handle is None:
             handle = build_handle(self, metadata[0], counts[0], expand, expert_alignment, x.dtype, main_sms)

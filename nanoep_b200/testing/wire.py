@@ -48,6 +48,7 @@ def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_expe
     out["ret_stride"] = align(topk * max_tokens * hidden * 2, region)
     out["ret_offset"] = take(2 * out["ret_stride"])
     out["meta_scratch_offset"] = take(ranks * max_tokens * (topk + 2) * 4)
+    out["slot_scratch_offset"] = take((ranks * max_tokens * topk + local * 128) * 4)
     out["num_bytes"] = at
     out["row_bytes"] = wire_row_bytes(hidden, topk)
     out["msg_ints"] = count_message_ints(local)

@@ -27,7 +27,7 @@ def main():
         with CudaBuffer(dist.group.WORLD, cfg) as buf:
             for variant, (fuse, overlap) in enumerate([(False, False), (True, False), (False, True), (True, True)]):
                 layer = ExpertParallelMoE(buf, w13_all[rank * L:(rank + 1) * L].contiguous(), w2_all[rank * L:(rank + 1) * L].contiguous(),
-                                          fuse_combine=fuse, overlap_dispatch=overlap, comm_sms=16)
+                                          fuse_combine=fuse, overlap_dispatch=overlap)
                 for it, routing in enumerate((balanced_routing, zipf_routing)):
                     idx, w = routing(T - rank, E, K, seed=31 * it + rank)
                     x = (torch.randn(T - rank, H, generator=torch.Generator().manual_seed(100 + rank + it)) * 0.5).to(torch.bfloat16)
