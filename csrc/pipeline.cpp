@@ -114,19 +114,32 @@ const P* upload(const std::vector<P>& host, std::vector<at::Tensor>& keep, cudaS
 
 struct Streams {
     c10::cuda::CUDAStream compute, comm;
+    c10::cuda::CUDAStream work;  // where this operation's kernels run
 };
 
-Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device) {
+// Asynchronous operations run on the buffer's communication stream behind the caller's stream (or
+// behind `previous_event`).  Synchronous operations run directly on the caller's stream - no stream
+// hop on either side, which is what small (decode-size) calls are made of - after whatever earlier
+// asynchronous operation is still on the communication stream, so operations of one rank never overlap.
+Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bool async_op) {
     auto compute = c10::cuda::getCurrentCUDAStream(device);
     auto comm = c10::cuda::getStreamFromExternal(reinterpret_cast<cudaStream_t>(comm_handle), device);
-    if (previous_event != -1) {
-        cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
-    } else {
-        at::cuda::CUDAEvent ready;
-        ready.record(compute);
-        ready.block(comm);
+    if (async_op) {
+        if (previous_event != -1) {
+            cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
+        } else {
+            at::cuda::CUDAEvent ready;
+            ready.record(compute);
+            ready.block(comm);
+        }
+        return Streams{compute, comm, comm};
     }
-    return Streams{compute, comm};
+    if (previous_event != -1)
+        cuda_check(cudaStreamWaitEvent(compute.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
+    at::cuda::CUDAEvent tail;
+    tail.record(comm);
+    tail.block(compute);
+    return Streams{compute, comm, compute};
 }
 
 void validate_group(const std::vector<PeerWindow*>& wins) {
@@ -140,19 +153,14 @@ void validate_group(const std::vector<PeerWindow*>& wins) {
 }
 
 std::shared_ptr<CompletionEvent> finish(const Streams& s, bool async_op, std::vector<at::Tensor> inputs, std::vector<at::Tensor> results) {
-    if (async_op) {
-        // Inputs were produced on another stream's pool; tell the allocator the comm stream used them.
-        for (auto& t : inputs)
-            if (t.defined() && t.numel() > 0) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), s.comm);
-        auto done = std::make_shared<CompletionEvent>();
-        done->event.record(s.comm);
-        done->protect = std::move(results);
-        return done;
-    }
-    at::cuda::CUDAEvent done;
-    done.record(s.comm);
-    done.block(s.compute);
-    return nullptr;
+    if (!async_op) return nullptr;  // the work already sits on the caller's stream
+    // Inputs were produced on another stream's pool; tell the allocator the comm stream used them.
+    for (auto& t : inputs)
+        if (t.defined() && t.numel() > 0) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), s.comm);
+    auto done = std::make_shared<CompletionEvent>();
+    done->event.record(s.comm);
+    done->protect = std::move(results);
+    return done;
 }
 
 }  // namespace
@@ -197,11 +205,11 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
     if (fresh) {
         cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-        cuda_check(cudaStreamIsCapturing(reinterpret_cast<cudaStream_t>(comm_stream), &capture), "capture query");
+        cuda_check(cudaStreamIsCapturing(c10::cuda::getCurrentCUDAStream(device).stream(), &capture), "capture query");
         TORCH_CHECK(capture == cudaStreamCaptureStatusNone, "fresh dispatch cannot be captured in a CUDA graph (it waits for counts on the host)");
     }
 
-    const Streams s = order_inputs(comm_stream, previous_event, device);
+    const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
     // Outputs live in the consumer stream's pool: the caller's stream when the call completes on it,
     // the comm stream when completion is handed over through an event.
     const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
@@ -217,7 +225,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     std::vector<at::Tensor> keep;
     std::vector<StageParams> stage(n);
     std::vector<int> parity(n);
-    const cudaStream_t cs = s.comm.stream();
+    const cudaStream_t cs = s.work.stream();
 
     {
         c10::cuda::CUDAStreamGuard pool(consumer);
@@ -260,11 +268,15 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         }
     }
     {
-        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        c10::cuda::CUDAStreamGuard on_comm(s.work);
         const StageParams* dev = upload(stage, keep, cs);
         g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
-        cuda_check(launch_stage(dev, LaunchShape{int(2 * num_sms), n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
+        int64_t max_tokens_now = 0;
+        for (int i = 0; i < n; ++i) max_tokens_now = std::max<int64_t>(max_tokens_now, xs[i].size(0));
+        // 16 warps per block, 4 row quarters per token: small calls get small grids
+        const int stage_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * num_sms, (max_tokens_now * 4 + 15) / 16)));
+        cuda_check(launch_stage(dev, LaunchShape{stage_grid, n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
         g_marks.mark("stage", cs);
         if (fresh) {
             std::vector<PlanParams> plan(n);
@@ -344,11 +356,14 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         }
     }
     {
-        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        c10::cuda::CUDAStreamGuard on_comm(s.work);
         const PullParams* dev = upload(pull, keep, cs);
         g_marks.mark("host_gap", cs);
         PeerWindow::launches += 1;
-        cuda_check(launch_pull(dev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "pull launch");
+        int64_t max_items = 1;
+        for (int i = 0; i < n; ++i) max_items = std::max<int64_t>(max_items, expand ? out.counts[i].second : out.counts[i].first * L.ranks);
+        const int pull_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
+        cuda_check(launch_pull(dev, LaunchShape{pull_grid, n}, ring.warps, ring.smem_bytes, cs), "pull launch");
         g_marks.mark("pull", cs);
     }
     std::vector<at::Tensor> inputs, results;
@@ -408,9 +423,9 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     const RingPlan ring = plan_ring(int64_t(L.hidden) * 2, lim.smem_optin);
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
 
-    const Streams s = order_inputs(comm_stream, previous_event, device);
+    const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
     const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
-    const cudaStream_t cs = s.comm.stream();
+    const cudaStream_t cs = s.work.stream();
     const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device);
     const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
 
@@ -442,7 +457,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             p.round_partial = (expand && allow_multiple_reduction) ? 1 : 0;
         }
         {
-            c10::cuda::CUDAStreamGuard on_comm(s.comm);
+            c10::cuda::CUDAStreamGuard on_comm(s.work);
             g_marks.mark("begin", cs);
             PeerWindow::launches += 1;
             cuda_check(launch_local_combine(&p, LaunchShape{2 * lim.sms, 1}, cs), "local combine launch");
@@ -494,15 +509,22 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
         }
     }
     {
-        c10::cuda::CUDAStreamGuard on_comm(s.comm);
+        c10::cuda::CUDAStreamGuard on_comm(s.work);
         const PushParams* pdev = upload(push, keep, cs);
         g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
-        cuda_check(launch_push(pdev, LaunchShape{int(num_sms), n}, ring.warps, ring.smem_bytes, cs), "push launch");
+        int64_t max_items = 1, max_tokens_now = 1;
+        for (int i = 0; i < n; ++i) {
+            max_items = std::max<int64_t>(max_items, expand ? capacity[i] : meta[i][0].size(0) * L.ranks);
+            max_tokens_now = std::max<int64_t>(max_tokens_now, meta[i][5].size(0));
+        }
+        const int push_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
+        cuda_check(launch_push(pdev, LaunchShape{push_grid, n}, ring.warps, ring.smem_bytes, cs), "push launch");
         g_marks.mark("push", cs);
         const ReduceParams* rdev = upload(reduce, keep, cs);
         PeerWindow::launches += 1;
-        cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
+        const int reduce_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * lim.sms, (max_tokens_now + 15) / 16)));
+        cuda_check(launch_reduce(rdev, LaunchShape{reduce_grid, n}, cs), "reduce launch");
         g_marks.mark("reduce", cs);
     }
     std::vector<at::Tensor> inputs, results;
