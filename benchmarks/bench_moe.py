@@ -88,6 +88,8 @@ def gemm_only(args, device):
     for name, fn, flops in (
         ("up_swiglu", lambda: gg.grouped_gemm(a, w13, offsets, swiglu=True), 2.0 * rows * args.hidden * 2 * args.inter),
         ("up_swiglu_3stage", lambda: gg.grouped_gemm(a, w13, offsets, swiglu=True, stages=3), 2.0 * rows * args.hidden * 2 * args.inter),
+        ("up_swiglu_pair", lambda: gg.grouped_gemm(a, w13, offsets, swiglu=True, pair=True), 2.0 * rows * args.hidden * 2 * args.inter),
+        ("down_pair", lambda: gg.grouped_gemm(h, w2, offsets, pair=True), 2.0 * rows * args.hidden * args.inter),
         ("down", lambda: gg.grouped_gemm(h, w2, offsets), 2.0 * rows * args.hidden * args.inter),
         ("down_3stage", lambda: gg.grouped_gemm(h, w2, offsets, stages=3), 2.0 * rows * args.hidden * args.inter),
         ("cublas_up", lambda: torch.bmm(a.view(local, rows_per, args.hidden), w13.transpose(1, 2)), 2.0 * rows * args.hidden * 2 * args.inter),

@@ -897,9 +897,17 @@ template <typename Params>
 cudaError_t launch_pair(void (*single)(const Params), void (*multi)(const Params*), const Params* params, LaunchShape shape, int threads,
                         size_t smem, cudaStream_t stream) {
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(shape.ranks_y > 1 ? (const void*)multi : (const void*)single),
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
+        // Raise the kernel's dynamic shared-memory limit once per (kernel, device) and only when it grows.
+        static thread_local size_t granted[2][64] = {};
+        int device = 0;
+        cudaGetDevice(&device);
+        size_t& have = granted[shape.ranks_y > 1 ? 1 : 0][device & 63];
+        if (smem > have) {
+            cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(shape.ranks_y > 1 ? (const void*)multi : (const void*)single),
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return e;
+            have = smem;
+        }
     }
     const dim3 grid(shape.grid_x, shape.ranks_y > 1 ? shape.ranks_y : 1);
     if (shape.ranks_y > 1)

@@ -95,7 +95,7 @@ void bind_gemm(pybind11::module_& m) {
         "grouped_gemm",
         [](const at::Tensor& a, const at::Tensor& w, const at::Tensor& expert_offsets, at::Tensor& out, at::Tensor& status, int64_t mode,
            c10::optional<at::Tensor> tile_ready, c10::optional<at::Tensor> tile_expected, int64_t max_ctas, double timeout_s,
-           c10::optional<at::Tensor> row_scale, int64_t stages) {
+           c10::optional<at::Tensor> row_scale, int64_t stages, bool pair) {
             c10::cuda::CUDAGuard guard(a.device());
             TORCH_CHECK(mode == gemm::kPlain || mode == gemm::kSwiGLU, "mode must be 0 (plain) or 1 (SwiGLU)");
             auto g = prepare(a, w, expert_offsets, status, int(mode), timeout_s);
@@ -121,13 +121,21 @@ void bind_gemm(pybind11::module_& m) {
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;
             PeerWindow::launches += 1;
+            if (pair) {
+                TORCH_CHECK(!tile_ready.has_value(), "the CTA-pair kernel has no tile gating");
+                const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+                const int pair_grid = max_ctas > 0 ? std::min<int>(sms, int(max_ctas)) : sms;
+                cudaError_t pe = gemm::launch_pair(g.map_a, g.map_b, g.args, int(mode), pair_grid, c10::cuda::getCurrentCUDAStream().stream());
+                TORCH_CHECK(pe == cudaSuccess, "grouped GEMM (CTA pairs) launch failed: ", cudaGetErrorString(pe));
+                return;
+            }
             cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, int(mode), int(stages), grid, c10::cuda::getCurrentCUDAStream().stream());
             TORCH_CHECK(e == cudaSuccess, "grouped GEMM launch failed: ", cudaGetErrorString(e));
         },
         pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"), pybind11::arg("out"), pybind11::arg("status"),
         pybind11::arg("mode"), pybind11::arg("tile_ready") = c10::nullopt, pybind11::arg("tile_expected") = c10::nullopt,
         pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0, pybind11::arg("row_scale") = c10::nullopt,
-        pybind11::arg("stages") = 4);
+        pybind11::arg("stages") = 4, pybind11::arg("pair") = false);
 
     // Down projection fused with the combine push: row r of (A @ W[e]^T) * slot_weight[r] is stored
     // (bf16) into the return partition of the row's source rank; padding rows are skipped.

@@ -104,11 +104,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -311,35 +314,44 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
             const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(acc * BN);
             if (kMode == kSwiGLU) {
                 __nv_bfloat16* out_row = args.out + int64_t(row) * args.ldo + nt * (BN / 2);
-#pragma unroll 1
-                for (int c = 0; c < BN / 2; c += 16) {
-                    uint32_t g[16], u[16];
-                    tmem_ld16(taddr + c, g);
-                    tmem_ld16(taddr + BN / 2 + c, u);
-                    tmem_ld_wait();
-                    uint32_t o[8];
+                // 32 gate + 32 up columns per step, the next step's TMEM loads in flight while this one is
+                // converted and stored
+                uint32_t g[2][32], u[2][32];
+                tmem_ld32(taddr, g[0]);
+                tmem_ld32(taddr + BN / 2, u[0]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float a = silu(__uint_as_float(g[2 * j])) * __uint_as_float(u[2 * j]);
-                        const float b = silu(__uint_as_float(g[2 * j + 1])) * __uint_as_float(u[2 * j + 1]);
+                for (int step = 0; step < BN / 2 / 32; ++step) {
+                    const int cur = step & 1, c = step * 32;
+                    tmem_ld_wait();
+                    if (step + 1 < BN / 2 / 32) {
+                        tmem_ld32(taddr + c + 32, g[cur ^ 1]);
+                        tmem_ld32(taddr + BN / 2 + c + 32, u[cur ^ 1]);
+                    }
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float a = silu(__uint_as_float(g[cur][2 * j])) * __uint_as_float(u[cur][2 * j]);
+                        const float b = silu(__uint_as_float(g[cur][2 * j + 1])) * __uint_as_float(u[cur][2 * j + 1]);
                         o[j] = pack_bf16(a, b);
                     }
-                    st_v4(out_row + c, o[0], o[1], o[2], o[3]);
-                    st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) st_v4(out_row + c + q * 8, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
                 }
             } else if (kMode == kPlain) {
                 __nv_bfloat16* out_row = args.out + int64_t(row) * args.ldo + nt * BN;
                 const float scale = args.row_scale != nullptr ? args.row_scale[row] : 1.f;
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(taddr + c, v);
-                    tmem_ld_wait();
-                    uint32_t o[8];
+                uint32_t v[2][32];
+                tmem_ld32(taddr, v[0]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
-                    st_v4(out_row + c, o[0], o[1], o[2], o[3]);
-                    st_v4(out_row + c + 8, o[4], o[5], o[6], o[7]);
+                for (int step = 0; step < BN / 32; ++step) {
+                    const int cur = step & 1, c = step * 32;
+                    tmem_ld_wait();
+                    if (step + 1 < BN / 32) tmem_ld32(taddr + c + 32, v[cur ^ 1]);
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o[j] = pack_bf16(__uint_as_float(v[cur][2 * j]) * scale, __uint_as_float(v[cur][2 * j + 1]) * scale);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) st_v4(out_row + c + q * 8, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
                 }
             } else {
                 // kScatter: acc * gate weight -> bf16 row in shared memory -> one 512-byte bulk store into
@@ -360,16 +372,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
                 uint8_t* my_row = out_stage + (quarter * 32 + lane) * kOutPitch;
                 // the previous tile's bulk store must have finished reading this row buffer
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(taddr + c, v);
-                    tmem_ld_wait();
-                    uint32_t o[8];
+                uint32_t v[2][32];
+                tmem_ld32(taddr, v[0]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
-                    st_shared_v4(my_row + c * 2, o[0], o[1], o[2], o[3]);
-                    st_shared_v4(my_row + c * 2 + 16, o[4], o[5], o[6], o[7]);
+                for (int step = 0; step < BN / 32; ++step) {
+                    const int cur = step & 1, c = step * 32;
+                    tmem_ld_wait();
+                    if (step + 1 < BN / 32) tmem_ld32(taddr + c + 32, v[cur ^ 1]);
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o[j] = pack_bf16(__uint_as_float(v[cur][2 * j]) * scale, __uint_as_float(v[cur][2 * j + 1]) * scale);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) st_shared_v4(my_row + c * 2 + q * 16, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (out_row != nullptr) bulk_store_row(out_row, my_row, kOutRowBytes);

@@ -38,7 +38,7 @@ def check_status(device=None):
 
 
 def grouped_gemm(a, w, expert_offsets, *, swiglu: bool = False, out=None, tile_ready=None, tile_expected=None, max_ctas: int = 0,
-                 timeout_s: float = 5.0, row_scale=None, stages: int = 4) -> torch.Tensor:
+                 timeout_s: float = 5.0, row_scale=None, stages: int = 4, pair: bool = False) -> torch.Tensor:
     """``out[r] = a[r] @ w[e(r)].T`` (bf16 in, fp32 accumulate, bf16 out).
 
     a: ``[rows, K]`` bf16, rows % 128 == 0;  w: ``[E, N, K]`` bf16 (``[E, 2*I, K]`` gate rows then up
@@ -46,12 +46,13 @@ def grouped_gemm(a, w, expert_offsets, *, swiglu: bool = False, out=None, tile_r
     With ``swiglu`` the result is ``silu(a @ w_gate.T) * (a @ w_up.T)`` of shape ``[rows, I]``.
     ``row_scale`` (fp32 ``[rows]``, plain mode) multiplies each output row in FP32 before the bf16 round.
     ``stages=3`` shrinks the operand pipeline so that a transfer kernel can share the SMs.
+    ``pair=True`` runs the CTA-pair kernel (tcgen05 ``cta_group::2``: two SMs share every weight tile).
     """
     n_out = w.shape[1] // 2 if swiglu else w.shape[1]
     if out is None:
         out = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
     _ext().grouped_gemm(a, w, expert_offsets, out, status_tensor(a.device), SWIGLU if swiglu else PLAIN, tile_ready, tile_expected,
-                        int(max_ctas), float(timeout_s), row_scale, int(stages))
+                        int(max_ctas), float(timeout_s), row_scale, int(stages), bool(pair))
     return out
 
 

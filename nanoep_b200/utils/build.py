@@ -31,6 +31,7 @@ SOURCES = (
     "peer_window.cu",
     "ep_kernels.cu",
     "grouped_gemm_sm100.cu",
+    "grouped_gemm_sm100_2cta.cu",
 )
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

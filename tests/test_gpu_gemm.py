@@ -88,3 +88,28 @@ def test_tile_gating_waits_for_ready_counters():
     with pytest.raises(RuntimeError, match="timed out"):
         gg.check_status()
     assert torch.ones(2, device="cuda").sum().item() == 2
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_cta_pair_kernel_matches_reference_and_single_cta(swiglu):
+    """tcgen05 cta_group::2 variant: experts with odd and even block counts, an empty expert, many tiles."""
+    torch.manual_seed(5)
+    blocks = [3, 2, 0, 1, 4, 5]
+    offsets = _offsets(blocks)
+    rows = int(offsets[-1])
+    K, N = 512, 512
+    a = (torch.randn(rows, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(len(blocks), N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    single = gg.grouped_gemm(a, w, offsets, swiglu=swiglu)
+    n_out = N // 2 if swiglu else N
+    out = torch.full((rows, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gg.grouped_gemm(a, w, offsets, swiglu=swiglu, pair=True, out=out)
+    torch.cuda.synchronize()
+    gg.check_status()
+    ref = gg.grouped_gemm_reference(a, w, offsets, swiglu=swiglu)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    assert torch.equal(out, single), "pair and single-CTA kernels accumulate in the same order"
+    small = gg.grouped_gemm(a, w, offsets, swiglu=swiglu, pair=True, max_ctas=4)
+    torch.cuda.synchronize()
+    gg.check_status()
+    assert torch.equal(small, single)
