@@ -143,7 +143,7 @@ void bind_gemm(pybind11::module_& m) {
         "grouped_gemm_scatter",
         [](PeerWindow& window, int64_t parity, const at::Tensor& a, const at::Tensor& w, const at::Tensor& expert_offsets,
            const at::Tensor& slot_map, const at::Tensor& recv_metadata, c10::optional<at::Tensor> slot_weights, at::Tensor& status,
-           int64_t max_ctas, double timeout_s) {
+           int64_t max_ctas, double timeout_s, bool pair) {
             c10::cuda::CUDAGuard guard(a.device());
             auto g = prepare(a, w, expert_offsets, status, gemm::kScatter, timeout_s);
             const WindowLayout& L = window.layout();
@@ -168,12 +168,19 @@ void bind_gemm(pybind11::module_& m) {
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;
             PeerWindow::launches += 1;
-            cudaError_t e = gemm::launch(g.map_a, g.map_b, g.args, gemm::kScatter, 3, grid, c10::cuda::getCurrentCUDAStream().stream());
+            cudaError_t e;
+            if (pair) {
+                const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+                e = gemm::launch_pair(g.map_a, g.map_b, g.args, gemm::kScatter, max_ctas > 0 ? std::min<int>(sms, int(max_ctas)) : sms,
+                                      c10::cuda::getCurrentCUDAStream().stream());
+            } else {
+                e = gemm::launch(g.map_a, g.map_b, g.args, gemm::kScatter, 3, grid, c10::cuda::getCurrentCUDAStream().stream());
+            }
             TORCH_CHECK(e == cudaSuccess, "grouped GEMM (scatter) launch failed: ", cudaGetErrorString(e));
         },
         pybind11::arg("window"), pybind11::arg("parity"), pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"),
         pybind11::arg("slot_map"), pybind11::arg("recv_metadata"), pybind11::arg("slot_weights"), pybind11::arg("status"),
-        pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0);
+        pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0, pybind11::arg("pair") = true);
 
     m.def("gemm_kernel_registers", [](int64_t mode) { return gemm::kernel_registers(int(mode)); });
     m.def("gemm_shared_bytes", [](int64_t mode, int64_t stages) { return int64_t(gemm::shared_bytes(int(mode), int(stages))); });

@@ -29,13 +29,17 @@ namespace gemm {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int kStages = 6;
 constexpr int kABytes = BM * BK * 2;        // 16 KB: this CTA's activation rows
 constexpr int kBHalfBytes = BN / 2 * BK * 2;  // 16 KB: this CTA's half of the weight rows
 constexpr int kStageBytes = kABytes + kBHalfBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kMaxExperts = 1024;
+constexpr int kMaxStages = 6;
+// kScatter stages each 512-byte output row in shared memory (padded rows) before one bulk store.
+constexpr int kOutRowBytes = BN * 2;
+constexpr int kOutPitch = kOutRowBytes + 16;
+constexpr int kOutStageBytes = 4 * 32 * kOutPitch;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint64_t timer_ns() {
@@ -150,7 +154,7 @@ __device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t 
 }
 
 struct PairShared {
-    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+    uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort;
     int offsets[kMaxExperts + 1];     // row offsets
@@ -177,12 +181,20 @@ __device__ __forceinline__ PairTile locate_pair(const PairShared& sh, int expert
     return t;
 }
 
-template <int kMode>
+__device__ __forceinline__ void bulk_store_row(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int kMode, int kStages>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                         const __grid_constant__ CUtensorMap map_b, const Args args) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* tiles = smem;
     PairShared& sh = *reinterpret_cast<PairShared*>(smem + kStages * kStageBytes);
+    uint8_t* out_stage = smem + kStages * kStageBytes + ((sizeof(PairShared) + 127) / 128) * 128;  // kScatter only
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();
     const bool leader = cta == 0;
@@ -346,6 +358,40 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_pair_kernel(const __
 #pragma unroll
                         for (int q = 0; q < 4; ++q) st_v4(out_row + c + q * 8, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
                     }
+                } else if (kMode == kScatter) {
+                    // acc * gate weight -> bf16 row in shared memory -> one 512-byte bulk store into the
+                    // source rank's return partition (peer memory over NVLink, or local); padding rows skipped
+                    __nv_bfloat16* out_row = nullptr;
+                    float scale = 1.f;
+                    const int a = args.slot_map[row];
+                    if (a >= 0) {
+                        const int recv_row = a / args.topk, k = a % args.topk;
+                        const int* meta = args.recv_metadata + int64_t(recv_row) * (args.topk + 2);
+                        const int src = meta[0], tok = meta[1];
+                        scale = args.slot_weights != nullptr ? args.slot_weights[row] : 1.f;
+                        out_row = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(args.peers[src]) + args.ret_offset +
+                                                                   (int64_t(k) * args.max_tokens + tok) * int64_t(args.ldo) * 2) +
+                                  nt * BN;
+                    }
+                    uint8_t* my_row = out_stage + (quarter * 32 + lane) * kOutPitch;
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    uint32_t v[2][32];
+                    tmem_ld32(taddr, v[0]);
+#pragma unroll
+                    for (int step = 0; step < BN / 32; ++step) {
+                        const int cur = step & 1, c = step * 32;
+                        tmem_ld_wait();
+                        if (step + 1 < BN / 32) tmem_ld32(taddr + c + 32, v[cur ^ 1]);
+                        uint32_t o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            o[j] = pack_bf16(__uint_as_float(v[cur][2 * j]) * scale, __uint_as_float(v[cur][2 * j + 1]) * scale);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) st_shared_v4(my_row + c * 2 + q * 16, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (out_row != nullptr) bulk_store_row(out_row, my_row, kOutRowBytes);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 } else {
                     __nv_bfloat16* out_row = args.out + int64_t(row) * args.ldo + nt * BN;
                     const float scale = args.row_scale != nullptr ? args.row_scale[row] : 1.f;
@@ -369,6 +415,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_pair_kernel(const __
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh.tmem_empty[acc]), 0));
         }
+        if (kMode == kScatter) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __threadfence_system();
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -379,10 +429,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_pair_kernel(const __
     }
 }
 
-template <int kMode>
+template <int kMode, int kStages>
 cudaError_t launch_pair_mode(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int grid, cudaStream_t stream) {
-    auto* fn = grouped_gemm_pair_kernel<kMode>;
-    const size_t smem = size_t(kStages) * kStageBytes + sizeof(PairShared) + 256;
+    auto* fn = grouped_gemm_pair_kernel<kMode, kStages>;
+    const size_t smem = size_t(kStages) * kStageBytes + ((sizeof(PairShared) + 127) / 128) * 128 + (kMode == kScatter ? kOutStageBytes : 0) + 256;
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t config{};
@@ -402,13 +452,15 @@ cudaError_t launch_pair_mode(const CUtensorMap& a, const CUtensorMap& b, const A
 
 }  // namespace
 
-// `grid` is rounded down to an even number of CTAs (one cluster = two CTAs on two SMs).
+// `grid` is rounded down to an even number of CTAs (one cluster = two CTAs on two SMs).  Plain and
+// SwiGLU run six operand stages; the scatter epilogue needs shared memory for its row staging and runs four.
 cudaError_t launch_pair(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream) {
     if (args.num_experts > kMaxExperts) return cudaErrorInvalidValue;
     grid &= ~1;
     if (grid < 2) return cudaErrorInvalidValue;
-    if (mode == kPlain) return launch_pair_mode<kPlain>(a, b, args, grid, stream);
-    if (mode == kSwiGLU) return launch_pair_mode<kSwiGLU>(a, b, args, grid, stream);
+    if (mode == kPlain) return launch_pair_mode<kPlain, 6>(a, b, args, grid, stream);
+    if (mode == kSwiGLU) return launch_pair_mode<kSwiGLU, 6>(a, b, args, grid, stream);
+    if (mode == kScatter) return launch_pair_mode<kScatter, 4>(a, b, args, grid, stream);
     return cudaErrorInvalidValue;
 }
 

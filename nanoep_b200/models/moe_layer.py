@@ -30,7 +30,7 @@ ALIGNMENT = 128
 
 class ExpertParallelMoE:
     def __init__(self, buffer: CudaBuffer, w13: torch.Tensor, w2: torch.Tensor, *, fuse_combine: bool = True,
-                 overlap_dispatch: bool = True, comm_ring_bytes: int = 72 * 1024):
+                 overlap_dispatch: bool = False, comm_ring_bytes: int = 72 * 1024, cta_pairs: bool | None = None):
         cfg = buffer.config
         local = cfg.num_experts // buffer.world_size
         if w13.dim() != 3 or w13.shape[0] != local or w13.shape[2] != cfg.hidden or w13.shape[1] % 256:
@@ -49,6 +49,11 @@ class ExpertParallelMoE:
         self.device = w13.device
         self.device_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.comm_ring_bytes = int(comm_ring_bytes)
+        # tcgen05 cta_group::2 kernels (two SMs share each weight tile).  None = decide per call: a pair
+        # needs two row blocks of the same expert, so with few blocks per expert the half-empty last
+        # pairs cost more than the shared weight tiles save.
+        self.cta_pairs = cta_pairs
+        self.local_experts = local
         rows_cap = buffer.world_size * cfg.num_max_tokens_per_rank * min(cfg.num_topk, local) + local * (ALIGNMENT - 1)
         blocks = rows_cap // ALIGNMENT + 2
         self._tile_ready = torch.zeros(blocks, dtype=torch.int32, device=self.device)
@@ -80,6 +85,9 @@ class ExpertParallelMoE:
             ring_smem_limit=self.comm_ring_bytes if overlap else 0,
         )
         h_in, offsets = got.x, got.handle.layout.expert_offsets
+        pairs = self.cta_pairs
+        if pairs is None:
+            pairs = got.handle.layout.expanded_capacity >= 6 * ALIGNMENT * self.local_experts
         if overlap:
             # The GEMM must not wait for the whole dispatch: it is gated per row block by the counters.
             h_in.record_stream(stream)
@@ -92,20 +100,20 @@ class ExpertParallelMoE:
             mark("dispatch+up_gemm")
         else:
             mark("dispatch")
-            h = gg.grouped_gemm(h_in, self.w13, offsets, swiglu=True)
+            h = gg.grouped_gemm(h_in, self.w13, offsets, swiglu=True, pair=pairs)
             mark("up_gemm")
         self.last_handle = got.handle
         if self.fuse_combine:
             window = buf.window
             parity = self._ext.next_combine_parity(window)
             self._ext.grouped_gemm_scatter(window, parity, h, self.w2, offsets, got.handle.slot_map, got.handle.layout.recv_metadata,
-                                           got.topk_weights, gg.status_tensor(self.device), 0, 5.0)
+                                           got.topk_weights, gg.status_tensor(self.device), 0, 5.0, pairs)
             mark("down_gemm_scatter")
             out = self._ext.combine_finish([window], [handle_metadata(got.handle)], [parity], [bias])[0]
             mark("barrier+reduce")
             self._collect(marks)
             return out
-        y = gg.grouped_gemm(h, self.w2, offsets, row_scale=got.topk_weights)  # gate weight in FP32 in the epilogue
+        y = gg.grouped_gemm(h, self.w2, offsets, row_scale=got.topk_weights, pair=pairs)  # gate weight in FP32 in the epilogue
         mark("down_gemm")
         out = buf.combine(y, got.handle, bias=bias).x
         mark("combine")
