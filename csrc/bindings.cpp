@@ -16,8 +16,8 @@ py::dict layout_dict(const nep::WindowLayout& w) {
     d["ctrl_offset"] = w.ctrl_offset;
     d["counts_in_offset"] = w.counts_in_offset;
     d["counts_in_stride"] = w.counts_in_stride;
-    d["stage_topk_offset"] = w.stage_topk_offset;
-    d["stage_topk_stride"] = w.stage_topk_stride;
+    d["routing_in_offset"] = w.routing_in_offset;
+    d["routing_in_stride"] = w.routing_in_stride;
     d["stage_rows_offset"] = w.stage_rows_offset;
     d["stage_rows_stride"] = w.stage_rows_stride;
     d["ret_w_offset"] = w.ret_w_offset;

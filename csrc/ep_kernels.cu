@@ -57,7 +57,8 @@ __device__ void stage_body(const StageParams& p) {
         __syncthreads();
     }
     char* rows = win + L.stage_rows_offset + int64_t(p.parity) * L.stage_rows_stride;
-    int* stage_topk = reinterpret_cast<int*>(win + L.stage_topk_offset + int64_t(p.parity) * L.stage_topk_stride);
+    // this rank's slice of every receiver's routing table
+    const int64_t routing_slice = L.routing_in_offset + int64_t(p.parity) * L.routing_in_stride + int64_t(p.c.rank) * L.max_tokens * K * 4;
     const int64_t rb = L.row_bytes();
     const int vecs = H / 8;  // 16-byte chunks per row
 
@@ -97,7 +98,8 @@ __device__ void stage_body(const StageParams& p) {
                 } else if (raw != -1) {
                     report(status, kBadExpertId, uint32_t(t), kTagStage);
                 }
-                stage_topk[int64_t(t) * K + lane] = e;
+                // Publish the routing to every rank (itself included): receivers plan from local memory.
+                for (int d = 0; d < R; ++d) reinterpret_cast<int*>(window(p.c, d) + routing_slice)[int64_t(t) * K + lane] = e;
             }
             const unsigned vmask = __ballot_sync(kFull, valid);
             const int d = valid ? e / Le : -1;
@@ -208,7 +210,7 @@ __device__ void stage_body(const StageParams& p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// plan (fresh dispatch): every receiver scans all sources' staged routing in chunks of 32 tokens,
+// plan (fresh dispatch): every receiver scans the routing all sources wrote into its window, 32 tokens at a time,
 // keeps the tokens that chose one of its experts, and assigns a receive row (grouped by source
 // rank) and, in the expert-major layout, one slot per local choice.
 // ------------------------------------------------------------------------------------------
@@ -244,8 +246,8 @@ __device__ void plan_body(const PlanParams& p) {
         if (tok0 >= Ts) continue;
         const int n_tok = min(32, Ts - tok0);
         const int n = n_tok * K;
-        const int* remote =
-            reinterpret_cast<const int*>(window(p.c, s) + L.stage_topk_offset + int64_t(p.parity) * L.stage_topk_stride) + int64_t(tok0) * K;
+        const int* remote = reinterpret_cast<const int*>(window(p.c, p.c.rank) + L.routing_in_offset + int64_t(p.parity) * L.routing_in_stride) +
+                            (int64_t(s) * L.max_tokens + tok0) * K;
         __syncwarp();
         for (int base = 0; base < n; base += 256) {
             int v[8];

@@ -42,8 +42,8 @@ struct WindowLayout {
     int64_t ctrl_offset;         // local scratch: tickets, count accumulators, cursors, prefixes
     int64_t counts_in_offset;    // [2] i32[R][2+L]  count messages written by the sources
     int64_t counts_in_stride;
-    int64_t stage_topk_offset;   // [2] i32[Tmax][K] this rank's routing, read by the receivers
-    int64_t stage_topk_stride;
+    int64_t routing_in_offset;   // [2] i32[R][Tmax][K] every source's routing, written by the sources
+    int64_t routing_in_stride;
     int64_t stage_rows_offset;   // [2] u8[Tmax][wire_row_bytes] staged tokens, pulled by the receivers
     int64_t stage_rows_stride;
     int64_t ret_w_offset;        // [2] f32[Tmax][K] gate-weight payload returned by combine
@@ -96,8 +96,8 @@ struct WindowLayout {
         w.ctrl_offset = take(w.ctrl_ints() * 4);
         w.counts_in_stride = align_up(int64_t(ranks) * w.msg_ints() * 4, kRegionAlign);
         w.counts_in_offset = take(2 * w.counts_in_stride);
-        w.stage_topk_stride = align_up(max_tokens * topk * 4, kRegionAlign);
-        w.stage_topk_offset = take(2 * w.stage_topk_stride);
+        w.routing_in_stride = align_up(int64_t(ranks) * max_tokens * topk * 4, kRegionAlign);
+        w.routing_in_offset = take(2 * w.routing_in_stride);
         w.stage_rows_stride = align_up(max_tokens * w.row_bytes(), kRegionAlign);
         w.stage_rows_offset = take(2 * w.stage_rows_stride);
         w.ret_w_stride = align_up(max_tokens * topk * 4, kRegionAlign);

@@ -19,6 +19,7 @@ from torch.utils import deterministic
 from ..config import EPConfig
 from ..types import NativeCombineResult, NativeDispatchResult, NativeHandle, NativeLayout
 from ..utils.sms import nvlink_gbs, theoretical_num_sms
+from ..utils.tracing import nvtx_range
 from . import bootstrap
 
 
@@ -222,7 +223,7 @@ class CudaBuffer:
 
         cached_metadata, cached_capacity = ([], 0) if handle is None else (handle_metadata(handle), handle.layout.expanded_capacity)
         main_sms = self._resolve_num_sms(num_sms, handle)
-        with torch.cuda.device(self._device):
+        with torch.cuda.device(self._device), nvtx_range("nanoep.dispatch.fresh" if handle is None else "nanoep.dispatch.cached"):
             outputs, metadata, counts, completed = self._backend.dispatch(
                 [self._window],
                 [x],
@@ -275,7 +276,7 @@ class CudaBuffer:
             raise ValueError("combine handle configuration does not match this CudaBuffer")
         validate_combine_inputs(self._config, handle, x, weights, bias, torch.device("cuda", self._device))
         main_sms = self._resolve_num_sms(num_sms, handle)
-        with torch.cuda.device(self._device):
+        with torch.cuda.device(self._device), nvtx_range("nanoep.combine"):
             outputs, completed = self._backend.combine(
                 [self._window],
                 [x],

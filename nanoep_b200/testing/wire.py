@@ -39,8 +39,8 @@ def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_expe
     out["ctrl_offset"] = take(ctrl_ints * 4)
     out["counts_in_stride"] = align(ranks * count_message_ints(local) * 4, region)
     out["counts_in_offset"] = take(2 * out["counts_in_stride"])
-    out["stage_topk_stride"] = align(max_tokens * topk * 4, region)
-    out["stage_topk_offset"] = take(2 * out["stage_topk_stride"])
+    out["routing_in_stride"] = align(ranks * max_tokens * topk * 4, region)
+    out["routing_in_offset"] = take(2 * out["routing_in_stride"])
     out["stage_rows_stride"] = align(max_tokens * wire_row_bytes(hidden, topk), region)
     out["stage_rows_offset"] = take(2 * out["stage_rows_stride"])
     out["ret_w_stride"] = align(max_tokens * topk * 4, region)
