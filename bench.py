@@ -57,31 +57,74 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons of one GPU while the timed region runs.
+
+    Uses NVML (read-only queries, a sample every few milliseconds) and falls back to ``nvidia-smi`` when
+    the Python bindings are missing.  Nothing is ever set or reset.
+    """
 
     QUERY = (
         "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.005):
         self.gpu_index = gpu_index
-        self.samples: list[list[str]] = []
+        self.gpu_uuid = gpu_uuid
+        self.period_s = period_s
+        self.samples: list[tuple[float, float, list[str]]] = []  # (sm MHz, max MHz, active reasons)
         self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            if gpu_uuid:
+                uuid = gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            else:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self._nvml = pynvml
+        except Exception:  # noqa: BLE001 - fall back to nvidia-smi
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        sm = float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
+        mx = float(n.nvmlDeviceGetMaxClockInfo(self._handle, n.NVML_CLOCK_SM))
+        mask = int(n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") else int(
+            n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        names = []
+        for name, attr in (("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+                           ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap")):
+            bit = getattr(n, attr, None)
+            if bit is not None and mask & int(bit):
+                names.append(name)
+        self.samples.append((sm, mx, names))
+
+    def _sample_smi(self):
+        target = self.gpu_uuid if self.gpu_uuid else str(self.gpu_index)
+        out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", target],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        if not out:
+            return
+        f = [v.strip() for v in out.splitlines()[0].split(",")]
+        names = [name for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8])
+                 if flag.lower().startswith("active")]
+        self.samples.append((float(f[1]), float(f[2]), names))
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.gpu_index)],
-                    capture_output=True, text=True, timeout=5,
-                ).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.splitlines()[0].split(",")])
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:  # noqa: BLE001 - sampling is best effort
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(self.period_s if self._nvml is not None else 0.2)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -93,21 +136,15 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self) -> dict:
-        sm, mx, reasons = [], [], set()
-        for s in self.samples:
-            try:
-                sm.append(float(s[1]))
-                mx.append(float(s[2]))
-            except (ValueError, IndexError):
-                continue
-            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[4:8]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
+        sm = [s[0] for s in self.samples]
+        mx = [s[1] for s in self.samples]
+        reasons = sorted({r for s in self.samples for r in s[2]})
         return {
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_max_mhz": max(mx) if mx else None,
-            "reasons": sorted(reasons),
+            "reasons": reasons,
             "samples": len(sm),
+            "source": "nvml" if self._nvml is not None else "nvidia-smi",
         }
 
 
@@ -193,7 +230,7 @@ def run_ours(args, rank, world, device, control_group):
             ext.take_phase_timings()
             ext.set_phase_timing(True)
         sync_all()
-        with ClockSampler(device.index) as clocks:
+        with ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid)) as clocks:
             wall0 = time.perf_counter()
             for i in range(args.steps):
                 xi = x_sets[i % len(x_sets)]
@@ -364,7 +401,7 @@ def run_nccl(args, rank, world, device, control_group):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     mids = []
-    with ClockSampler(device.index) as clocks:
+    with ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid)) as clocks:
         for i in range(args.steps):
             flush.fill_(i & 0xFF)
             starts[i].record()

@@ -5,6 +5,9 @@
                     then the cached handle is reused for 10 dispatch/combine pairs with async_op=True.
   --config decode   tokens/rank in {1, 8, 32, 128, 512, 4096}, hidden 7168, 256 experts, top-8, uniform
                     routing; p50/p99 latency of fresh dispatch, cached dispatch and combine.
+  --config published  the point of the reference's published figure: 256 tokens/rank, hidden 4096, top-8,
+                    bf16, expert-major layout (the figure does not state the expert count; 256 is used).
+                    Printed next to the reference's H20 numbers for the same GPU count.
 
 Latencies are CUDA-event times on the caller's stream (max over ranks of each percentile); rank 0
 prints one JSON line per measurement.  ``--impl nccl`` times torch.distributed all_to_all_single on
@@ -26,7 +29,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 
 def parse_args():
     p = argparse.ArgumentParser()
-    p.add_argument("--config", choices=("skew", "decode"), required=True)
+    p.add_argument("--config", choices=("skew", "decode", "published"), required=True)
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--iters", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
@@ -111,6 +114,8 @@ def main():
         else:
             H, E, K = 7168, 256, 8
             sizes = [int(t) for t in args.tokens.split(",")]
+            if args.config == "published":
+                H, sizes = 4096, [256]
             with CudaBuffer(control, EPConfig(E, K, H, max(sizes))) as buf:
                 for T in sizes:
                     idx, w = uniform_routing(T, E, K, seed=3 + rank)
@@ -160,7 +165,12 @@ def main():
                             cached.append(b0.elapsed_time(b1))
                             comb.append(c0.elapsed_time(c1))
                     buf.check_status()
-                    rec = {"bench": "decode", "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H}
+                    rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H}
+                    if args.config == "published":
+                        # reference figure (single-node H20): NanoEP / DeepEP 2.1.0 microseconds
+                        published = {2: (69.4, 40.2, 51.9), 4: (78.5, 54.9, 70.4), 8: (147.1, 91.8, 102.5)}.get(world)
+                        if published:
+                            rec["reference_h20_us"] = dict(zip(("fresh_dispatch", "cached_dispatch", "combine"), published))
                     for name, vals in (("fresh_dispatch", fresh), ("cached_dispatch", cached), ("combine", comb)):
                         rec[name + "_us_p50"] = reduce_max(statistics.median(vals)) * 1e3
                         rec[name + "_us_p99"] = reduce_max(percentile(vals, 0.99)) * 1e3
