@@ -68,7 +68,7 @@ class ClockSampler:
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.005):
+    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.002):
         self.gpu_index = gpu_index
         self.gpu_uuid = gpu_uuid
         self.period_s = period_s
@@ -127,6 +127,7 @@ class ClockSampler:
             self._stop.wait(self.period_s if self._nvml is not None else 0.2)
 
     def __enter__(self):
+        self._stop.clear()  # re-enterable: samples of all timed regions accumulate
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
         return self
@@ -284,6 +285,8 @@ def run_ours(args, rank, world, device, control_group):
             result_host = torch.empty(1, dtype=torch.float32).pin_memory()
             for phase, count in (("warm", 2), ("timed", args.steps)):
                 sync_all()
+                if phase == "timed":
+                    clocks.__enter__()  # keep sampling clocks during the end-to-end timed region as well
                 t0 = time.perf_counter()
                 ready = upload(0)
                 for i in range(count):
@@ -300,6 +303,7 @@ def run_ours(args, rank, world, device, control_group):
                     ready = nxt
                 sync_all()
                 elapsed = time.perf_counter() - t0
+            clocks.__exit__(None, None, None)
             e2e_ms = max_over_ranks(elapsed * 1e3) / args.steps
             e2e = {
                 "value": bytes_per_step / (e2e_ms * 1e-3) / 1e9,

@@ -44,6 +44,9 @@ def run_gemm():
     for _ in range(2):
         h = gg.grouped_gemm(a, w13, offsets, swiglu=True)
         y = gg.grouped_gemm(h, w2, offsets)
+    for _ in range(2):  # CTA-pair kernels (tcgen05 cta_group::2)
+        h = gg.grouped_gemm(a, w13, offsets, swiglu=True, pair=True)
+        y = gg.grouped_gemm(h, w2, offsets, pair=True)
     torch.cuda.synchronize()
     gg.check_status()
     print("gemm rows", a.shape[0], "flops up", 2 * a.shape[0] * H * 2 * I, "down", 2 * a.shape[0] * H * I)

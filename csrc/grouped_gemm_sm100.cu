@@ -371,23 +371,30 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
                 }
                 uint8_t* my_row = out_stage + (quarter * 32 + lane) * kOutPitch;
                 // the previous tile's bulk store must have finished reading this row buffer
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                // The row is sent as two 256-byte halves, each its own bulk group: before a half of the
+                // staging row is overwritten only the store that last read THAT half has to be done
+                // (wait_group.read 1 = everything but the newest group), so a store is always in flight.
                 uint32_t v[2][32];
                 tmem_ld32(taddr, v[0]);
 #pragma unroll
                 for (int step = 0; step < BN / 32; ++step) {
                     const int cur = step & 1, c = step * 32;
+                    if (step == 0 || step == BN / 64) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     tmem_ld_wait();
                     if (step + 1 < BN / 32) tmem_ld32(taddr + c + 32, v[cur ^ 1]);
                     uint32_t o[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) o[j] = pack_bf16(__uint_as_float(v[cur][2 * j]) * scale, __uint_as_float(v[cur][2 * j + 1]) * scale);
+                    for (int j = 0; j < 16; ++j)
+                        o[j] = pack_bf16(__uint_as_float(v[cur][2 * j]) * scale, __uint_as_float(v[cur][2 * j + 1]) * scale);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) st_shared_v4(my_row + c * 2 + q * 16, o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                    if (step == BN / 64 - 1 || step == BN / 32 - 1) {
+                        const int half = step == BN / 64 - 1 ? 0 : 1;
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        if (out_row != nullptr) bulk_store_row(out_row + half * (BN / 2), my_row + half * (kOutRowBytes / 2), kOutRowBytes / 2);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (out_row != nullptr) bulk_store_row(out_row, my_row, kOutRowBytes);
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
             tc_fence_before();
             __syncwarp();

@@ -142,6 +142,14 @@ Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bo
     return Streams{compute, comm, compute};
 }
 
+// Every operation carries its barrier epoch and buffer parity as kernel arguments, so a captured
+// launch could not be replayed; fail clearly instead of recording a graph that deadlocks later.
+void reject_graph_capture(int device, const char* why) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    cuda_check(cudaStreamIsCapturing(c10::cuda::getCurrentCUDAStream(device).stream(), &capture), "capture query");
+    TORCH_CHECK(capture == cudaStreamCaptureStatusNone, "nanoep_b200 operations cannot be captured in a CUDA graph: ", why);
+}
+
 void validate_group(const std::vector<PeerWindow*>& wins) {
     TORCH_CHECK(!wins.empty(), "no ranks given");
     const int n = int(wins.size());
@@ -203,11 +211,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     const int ring_budget = ring_smem_limit > 0 ? int(std::min<int64_t>(ring_smem_limit, lim.smem_optin)) : lim.smem_optin;
     const RingPlan ring = plan_ring(L.row_bytes(), ring_budget);
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
-    if (fresh) {
-        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-        cuda_check(cudaStreamIsCapturing(c10::cuda::getCurrentCUDAStream(device).stream(), &capture), "capture query");
-        TORCH_CHECK(capture == cudaStreamCaptureStatusNone, "fresh dispatch cannot be captured in a CUDA graph (it waits for counts on the host)");
-    }
+    reject_graph_capture(device, fresh ? "fresh dispatch waits for receive counts on the host" : "barrier epochs and buffer parities are kernel arguments");
 
     const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
     // Outputs live in the consumer stream's pool: the caller's stream when the call completes on it,
@@ -422,6 +426,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     TORCH_CHECK(num_sms >= 1 && num_sms <= lim.sms, "num_sms out of range");
     const RingPlan ring = plan_ring(int64_t(L.hidden) * 2, lim.smem_optin);
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
+    reject_graph_capture(device, "barrier epochs and buffer parities are kernel arguments");
 
     const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
     const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
