@@ -117,15 +117,16 @@ void bind_gemm(pybind11::module_& m) {
                             "row_scale must be float32 [rows] (plain mode only)");
                 g.args.row_scale = row_scale->data_ptr<float>();
             }
-            TORCH_CHECK(stages == 3 || stages == 4, "stages must be 3 or 4");
+            TORCH_CHECK(stages == 3 || stages == 4, "stages must be 3 or 4 (single-CTA) or 4 for the gated CTA-pair kernel");
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;
             PeerWindow::launches += 1;
             if (pair) {
-                TORCH_CHECK(!tile_ready.has_value(), "the CTA-pair kernel has no tile gating");
                 const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
                 const int pair_grid = max_ctas > 0 ? std::min<int>(sms, int(max_ctas)) : sms;
-                cudaError_t pe = gemm::launch_pair(g.map_a, g.map_b, g.args, int(mode), pair_grid, c10::cuda::getCurrentCUDAStream().stream());
+                // gated by tile counters = meant to share the SMs with the pull kernel: shorter pipeline
+                cudaError_t pe = gemm::launch_pair(g.map_a, g.map_b, g.args, int(mode), pair_grid, c10::cuda::getCurrentCUDAStream().stream(),
+                                                   tile_ready.has_value() ? 4 : 6);
                 TORCH_CHECK(pe == cudaSuccess, "grouped GEMM (CTA pairs) launch failed: ", cudaGetErrorString(pe));
                 return;
             }

@@ -41,7 +41,7 @@ size_t shared_bytes(int mode, int stages);
 cudaError_t launch(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int stages, int grid, cudaStream_t stream);
 int kernel_registers(int mode);
 // CTA-pair variant (tcgen05 cta_group::2, 256 x 256 tiles on two SMs); modes kPlain and kSwiGLU.
-cudaError_t launch_pair(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream);
+cudaError_t launch_pair(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream, int stages = 6);
 
 }  // namespace gemm
 }  // namespace nep

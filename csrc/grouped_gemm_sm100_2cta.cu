@@ -149,6 +149,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -256,6 +261,21 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_pair_kernel(const __
                     b_row = t.expert * args.b_rows_per_expert + nt * (BN / 2) + (cta ? args.swiglu_up_row_offset : 0);
                 else
                     b_row = t.expert * args.b_rows_per_expert + nt * BN + int(cta) * (BN / 2);
+                if (args.tile_ready != nullptr && t.valid) {
+                    // this CTA's rows are written by the dispatch pull of the same GPU; wait for all of them
+                    const int mb = t.row0 / BM;
+                    const int want = args.tile_expected[mb];
+                    const uint64_t start = timer_ns();
+                    while (ld_acquire_gpu(args.tile_ready + mb) < want) {
+                        __nanosleep(64);
+                        if (timer_ns() - start > limit_ns) {
+                            fail(kGemmTileTimeout);
+                            break;
+                        }
+                    }
+                    if (*abort_flag) break;
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(&sh.empty[stage], phase ^ 1u, limit_ns)) {
                         fail(kGemmPipeTimeout);
@@ -460,11 +480,13 @@ cudaError_t launch_pair_mode(const CUtensorMap& a, const CUtensorMap& b, const A
 
 // `grid` is rounded down to an even number of CTAs (one cluster = two CTAs on two SMs).  Plain and
 // SwiGLU run six operand stages; the scatter epilogue needs shared memory for its row staging and runs four.
-cudaError_t launch_pair(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream) {
+cudaError_t launch_pair(const CUtensorMap& a, const CUtensorMap& b, const Args& args, int mode, int grid, cudaStream_t stream, int stages) {
     if (args.num_experts > kMaxExperts) return cudaErrorInvalidValue;
     grid &= ~1;
     if (grid < 2) return cudaErrorInvalidValue;
     if (mode == kPlain) return launch_pair_mode<kPlain, 6>(a, b, args, grid, stream);
+    // four stages leave ~95 KB of shared memory per SM for a co-resident transfer kernel
+    if (mode == kSwiGLU && stages == 4) return launch_pair_mode<kSwiGLU, 4>(a, b, args, grid, stream);
     if (mode == kSwiGLU) return launch_pair_mode<kSwiGLU, 6>(a, b, args, grid, stream);
     if (mode == kScatter) return launch_pair_mode<kScatter, 4>(a, b, args, grid, stream);
     return cudaErrorInvalidValue;

@@ -30,7 +30,7 @@ ALIGNMENT = 128
 
 class ExpertParallelMoE:
     def __init__(self, buffer: CudaBuffer, w13: torch.Tensor, w2: torch.Tensor, *, fuse_combine: bool = True,
-                 overlap_dispatch: bool = False, comm_ring_bytes: int = 72 * 1024, cta_pairs: bool | None = None):
+                 overlap_dispatch: bool = False, comm_ring_bytes: int = 80 * 1024, cta_pairs: bool | None = None):
         cfg = buffer.config
         local = cfg.num_experts // buffer.world_size
         if w13.dim() != 3 or w13.shape[0] != local or w13.shape[2] != cfg.hidden or w13.shape[1] % 256:
@@ -95,7 +95,7 @@ class ExpertParallelMoE:
                 got.event.current_stream_wait()
                 mark("dispatch_small_ring")
             h = gg.grouped_gemm(h_in, self.w13, offsets, swiglu=True, tile_ready=self._tile_ready, tile_expected=self._tile_expected,
-                                stages=3)
+                                stages=3, pair=pairs)
             got.event.current_stream_wait()  # metadata and slot weights are complete from here on
             mark("dispatch+up_gemm")
         else:
