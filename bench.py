@@ -68,7 +68,7 @@ class ClockSampler:
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.002):
+    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.02):
         self.gpu_index = gpu_index
         self.gpu_uuid = gpu_uuid
         self.period_s = period_s

@@ -121,6 +121,14 @@ struct Streams {
 // behind `previous_event`).  Synchronous operations run directly on the caller's stream - no stream
 // hop on either side, which is what small (decode-size) calls are made of - after whatever earlier
 // asynchronous operation is still on the communication stream, so operations of one rank never overlap.
+// Two reusable events per thread for the stream hand-overs below (creating and destroying an event
+// per call costs microseconds, which small calls notice).
+cudaEvent_t handover_event(int slot) {
+    static thread_local cudaEvent_t events[2] = {nullptr, nullptr};
+    if (events[slot] == nullptr) cuda_check(cudaEventCreateWithFlags(&events[slot], cudaEventDisableTiming), "cudaEventCreate");
+    return events[slot];
+}
+
 Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bool async_op) {
     auto compute = c10::cuda::getCurrentCUDAStream(device);
     auto comm = c10::cuda::getStreamFromExternal(reinterpret_cast<cudaStream_t>(comm_handle), device);
@@ -128,17 +136,17 @@ Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bo
         if (previous_event != -1) {
             cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
         } else {
-            at::cuda::CUDAEvent ready;
-            ready.record(compute);
-            ready.block(comm);
+            cudaEvent_t ready = handover_event(0);
+            cuda_check(cudaEventRecord(ready, compute.stream()), "record caller stream");
+            cuda_check(cudaStreamWaitEvent(comm.stream(), ready, 0), "wait caller stream");
         }
         return Streams{compute, comm, comm};
     }
     if (previous_event != -1)
         cuda_check(cudaStreamWaitEvent(compute.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
-    at::cuda::CUDAEvent tail;
-    tail.record(comm);
-    tail.block(compute);
+    cudaEvent_t tail = handover_event(1);
+    cuda_check(cudaEventRecord(tail, comm.stream()), "record comm stream");
+    cuda_check(cudaStreamWaitEvent(compute.stream(), tail, 0), "wait comm stream");
     return Streams{compute, comm, compute};
 }
 

@@ -48,6 +48,27 @@ class CudaEvent:
         return self.event.query()
 
 
+class _OnDevice:
+    """``torch.cuda.device(index)`` costs several microseconds per use; ranks normally sit on their device
+    already, in which case this context manager does nothing."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.inner = None
+
+    def __enter__(self):
+        if torch.cuda.current_device() != self.index:
+            self.inner = torch.cuda.device(self.index)
+            self.inner.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.inner is not None:
+            self.inner.__exit__(*exc)
+            self.inner = None
+        return False
+
+
 def _load_native():
     from ..utils.build import load_extension
 
@@ -223,7 +244,7 @@ class CudaBuffer:
 
         cached_metadata, cached_capacity = ([], 0) if handle is None else (handle_metadata(handle), handle.layout.expanded_capacity)
         main_sms = self._resolve_num_sms(num_sms, handle)
-        with torch.cuda.device(self._device), nvtx_range("nanoep.dispatch.fresh" if handle is None else "nanoep.dispatch.cached"):
+        with _OnDevice(self._device), nvtx_range("nanoep.dispatch.fresh" if handle is None else "nanoep.dispatch.cached"):
             outputs, metadata, counts, completed = self._backend.dispatch(
                 [self._window],
                 [x],
@@ -276,7 +297,7 @@ class CudaBuffer:
             raise ValueError("combine handle configuration does not match this CudaBuffer")
         validate_combine_inputs(self._config, handle, x, weights, bias, torch.device("cuda", self._device))
         main_sms = self._resolve_num_sms(num_sms, handle)
-        with torch.cuda.device(self._device), nvtx_range("nanoep.combine"):
+        with _OnDevice(self._device), nvtx_range("nanoep.combine"):
             outputs, completed = self._backend.combine(
                 [self._window],
                 [x],

@@ -16,18 +16,37 @@ import os
 _ENABLED = os.environ.get("NANOEP_NVTX") == "1"
 
 
-@contextlib.contextmanager
-def nvtx_range(name: str):
-    if not _ENABLED:
-        yield
-        return
-    import torch
+class _NoRange:
+    def __enter__(self):
+        return self
 
-    torch.cuda.nvtx.range_push(name)
-    try:
-        yield
-    finally:
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
+class _Range:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+
+        torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+
         torch.cuda.nvtx.range_pop()
+        return False
+
+
+def nvtx_range(name: str):
+    """Context manager: an NVTX range when ``NANOEP_NVTX=1``, otherwise a shared no-op object."""
+    return _Range(name) if _ENABLED else _NO_RANGE
 
 
 @contextlib.contextmanager

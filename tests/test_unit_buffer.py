@@ -200,6 +200,7 @@ def make_buffer(monkeypatch):
     buf._comm_stream = SimpleNamespace(cuda_stream=77)
     buf._gpu_uuids = ("a", "b")
     monkeypatch.setattr(torch.cuda, "device", lambda d: __import__("contextlib").nullcontext())
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
     return buf
 
 
