@@ -21,6 +21,7 @@ import json
 import os
 import statistics
 import sys
+import time
 from datetime import timedelta
 from pathlib import Path
 
@@ -143,7 +144,7 @@ def main():
                         emit({"bench": "decode", "impl": "nccl_all_to_all_single (payload only, no routing)", "n_gpus": world, "tokens_per_rank": T,
                               "a2a_us_p50": reduce_max(statistics.median(times)) * 1e3, "a2a_us_p99": reduce_max(percentile(times, 0.99)) * 1e3})
                         continue
-                    fresh, cached, comb = [], [], []
+                    fresh, cached, comb, host_cached, host_comb = [], [], [], [], []
                     got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=True, alignment=1)
                     for it in range(args.warmup + args.iters):
                         dist.barrier(group=control)
@@ -153,17 +154,23 @@ def main():
                         a1.record()
                         b0, b1 = event_pair()
                         b0.record()
+                        h0 = time.perf_counter()
                         c = buf.dispatch(x, handle=got.handle, weights=w)
+                        h1 = time.perf_counter()
                         b1.record()
                         c0, c1 = event_pair()
                         c0.record()
+                        h2 = time.perf_counter()
                         back = buf.combine(c.x, got.handle)
+                        h3 = time.perf_counter()
                         c1.record()
                         torch.cuda.synchronize()
                         if it >= args.warmup:
                             fresh.append(a0.elapsed_time(a1))
                             cached.append(b0.elapsed_time(b1))
                             comb.append(c0.elapsed_time(c1))
+                            host_cached.append((h1 - h0) * 1e3)
+                            host_comb.append((h3 - h2) * 1e3)
                     buf.check_status()
                     rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H}
                     if args.config == "published":
@@ -171,6 +178,8 @@ def main():
                         published = {2: (69.4, 40.2, 51.9), 4: (78.5, 54.9, 70.4), 8: (147.1, 91.8, 102.5)}.get(world)
                         if published:
                             rec["reference_h20_us"] = dict(zip(("fresh_dispatch", "cached_dispatch", "combine"), published))
+                    # host time spent inside the calls (enqueue only, no device wait): the floor of the event latencies
+                    rec["host_call_us_p50"] = {"cached_dispatch": statistics.median(host_cached) * 1e3, "combine": statistics.median(host_comb) * 1e3}
                     for name, vals in (("fresh_dispatch", fresh), ("cached_dispatch", cached), ("combine", comb)):
                         rec[name + "_us_p50"] = reduce_max(statistics.median(vals)) * 1e3
                         rec[name + "_us_p99"] = reduce_max(percentile(vals, 0.99)) * 1e3

@@ -450,10 +450,17 @@ __device__ void pull_body(const PullParams& p) {
         __syncthreads();
     }
     if (p.expand) {
+        // Gap geometry is read 32 experts at a time (one coalesced load per lane) and handed round by
+        // shuffles: a scalar walk over the experts would cost one global-load latency per expert and warp.
         int base = 0;
-        for (int l = 0; l < Le; ++l) {
-            const int gs = int(p.expert_offsets[l] + p.expert_counts[l]);
-            const int len = int(p.expert_offsets[l + 1]) - gs;
+        for (int l0 = 0; l0 < Le; l0 += 32) {
+          const int my_l = l0 + lane;
+          const int my_gs = my_l < Le ? int(p.expert_offsets[my_l] + p.expert_counts[my_l]) : 0;
+          const int my_len = my_l < Le ? int(p.expert_offsets[my_l + 1]) - my_gs : 0;
+          const int in_wave = min(32, Le - l0);
+          for (int li = 0; li < in_wave; ++li) {
+            const int gs = __shfl_sync(kFull, my_gs, li);
+            const int len = __shfl_sync(kFull, my_len, li);
             int first = (gw - base) % GW;
             if (first < 0) first += GW;
             for (int j = first; j < len; j += GW) {
@@ -476,6 +483,7 @@ __device__ void pull_body(const PullParams& p) {
                 }
             }
             base = (base + len) % GW;
+          }
         }
     }
 

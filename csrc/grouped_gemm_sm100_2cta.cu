@@ -24,9 +24,13 @@
 
 #include <cuda_bf16.h>
 
+#include "tc_prim.cuh"
+
 namespace nep {
 namespace gemm {
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kABytes = BM * BK * 2;        // 16 KB: this CTA's activation rows
@@ -41,12 +45,6 @@ constexpr int kOutRowBytes = BN * 2;
 constexpr int kOutPitch = kOutRowBytes + 16;
 constexpr int kOutStageBytes = 4 * 32 * kOutPitch;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ uint64_t timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -62,36 +60,9 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 // arrive on a barrier given by its shared::cluster address (own or peer CTA)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done)
-                 : "r"(smem_u32(bar)), "r"(parity)
-                 : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
-    if (mbar_try(bar, parity)) return true;
-    const uint64_t start = timer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try(bar, parity))
-        if ((++spins & 1023u) == 0u && timer_ns() - start > limit_ns) return false;
-    return true;
-}
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
-    return pred != 0;
 }
 // 2-D tiled TMA load into this CTA's shared memory; completion bytes go to the barrier at
 // `bar_cluster_addr`, which may live in the peer CTA of the pair (unicast data path).
@@ -108,8 +79,6 @@ __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t co
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // completion of all earlier MMAs of the pair -> one arrival on the barrier at `bar_cluster_addr`
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
@@ -119,44 +88,8 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, ui
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
-    const uint32_t addr = smem_u32(tile);
-    uint64_t d = 0;
-    d |= uint64_t((addr >> 4) & 0x3FFF);
-    d |= uint64_t(1) << 16;
-    d |= uint64_t(1024 >> 4) << 32;
-    d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;
-    return d;
-}
-// bf16 x bf16 -> fp32, K-major operands, pair tile M = 256 (128 per CTA), N = 256.
-constexpr uint32_t kInstrDescPair = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t((2 * BM) >> 4) << 24);
-
-__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
+// pair tile: M = 256 (128 rows per CTA), N = 256
+constexpr uint32_t kInstrDescPair = instr_desc_bf16(2 * BM, BN);
 
 struct PairShared {
     uint64_t full[kMaxStages], empty[kMaxStages], tmem_full[2], tmem_empty[2];
@@ -184,13 +117,6 @@ __device__ __forceinline__ PairTile locate_pair(const PairShared& sh, int expert
     t.row0 = sh.offsets[lo] + block * BM;
     t.valid = t.row0 < sh.offsets[lo + 1];
     return t;
-}
-
-__device__ __forceinline__ void bulk_store_row(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void st_shared_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 template <int kMode, int kStages>

@@ -24,7 +24,7 @@ def test_no_cluster_multicast_loads_and_no_traps():
 
 
 def test_every_device_wait_is_bounded():
-    text = (ROOT / "csrc" / "prim.cuh").read_text() + (ROOT / "csrc" / "grouped_gemm_sm100.cu").read_text()
+    text = "".join((ROOT / "csrc" / name).read_text() for name in ("prim.cuh", "tc_prim.cuh", "grouped_gemm_sm100.cu", "grouped_gemm_sm100_2cta.cu"))
     # each spin loop compares a timer against a limit
     for loop in re.findall(r"while \((?:!mbar_try|ld_acquire)[^{]*\{?[^}]*", text):
         assert "timeout_ns" in loop or "limit_ns" in loop, loop
