@@ -617,27 +617,42 @@ __device__ void push_body(const PushParams& p) {
             const bool fine = live_row && checked_source(m, r, src, tok) && vm != 0;
             char* st = ring.slot(i);
             if (fine) {
-                for (int c = lane; c < vecs; c += 32) {
-                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                // four 16-byte column chunks x two slots per step: eight independent loads per lane in flight
+                for (int c0 = lane; c0 < vecs; c0 += 128) {
+                    float acc[4][8];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
                     unsigned left = vm;
                     while (left) {
-                        int k[4];
-                        int4 d[4];
+                        const int k0 = __ffs(left) - 1;
+                        left &= left - 1;
+                        const int k1 = left ? __ffs(left) - 1 : -1;
+                        if (left) left &= left - 1;
+                        const int slot0 = __shfl_sync(kFull, v, k0);
+                        const int slot1 = __shfl_sync(kFull, v, k1 < 0 ? 0 : k1);
+                        const int4* r0 = reinterpret_cast<const int4*>(p.y + int64_t(slot0) * H);
+                        const int4* r1 = reinterpret_cast<const int4*>(p.y + int64_t(slot1) * H);
+                        int4 d0[4], d1[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            k[j] = left ? __ffs(left) - 1 : -1;
-                            if (left) left &= left - 1;
+                        for (int u = 0; u < 4; ++u) {
+                            if (c0 + 32 * u < vecs) {
+                                d0[u] = ld_nc_v4(r0 + c0 + 32 * u);
+                                if (k1 >= 0) d1[u] = ld_nc_v4(r1 + c0 + 32 * u);
+                            }
                         }
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int slot = __shfl_sync(kFull, v, k[j] < 0 ? 0 : k[j]);
-                            if (k[j] >= 0) d[j] = ld_nc_v4(reinterpret_cast<const int4*>(p.y + int64_t(slot) * H) + c);
+                        for (int u = 0; u < 4; ++u) {
+                            if (c0 + 32 * u < vecs) {
+                                accumulate8(acc[u], d0[u]);
+                                if (k1 >= 0) accumulate8(acc[u], d1[u]);
+                            }
                         }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (k[j] >= 0) accumulate8(acc, d[j]);
                     }
-                    reinterpret_cast<int4*>(st)[c] = pack8(acc);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (c0 + 32 * u < vecs) reinterpret_cast<int4*>(st)[c0 + 32 * u] = pack8(acc[u]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
