@@ -9,6 +9,7 @@ Counterpart of the reference's tools/check_package.py:13-76.
 from __future__ import annotations
 
 import argparse
+import shutil
 import subprocess
 import sys
 import tempfile
@@ -24,7 +25,14 @@ def main():
     args = parser.parse_args()
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)
-        subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "-w", str(tmp / "dist"), str(ROOT)], check=True)
+        # build from a copy so that no build/ or egg-info directory appears in the checkout
+        src = tmp / "src"
+        src.mkdir()
+        for name in ("pyproject.toml", "setup.py", "MANIFEST.in", "README.md", "DESIGN.md"):
+            shutil.copy(ROOT / name, src / name)
+        shutil.copytree(ROOT / "csrc", src / "csrc")
+        shutil.copytree(ROOT / "nanoep_b200", src / "nanoep_b200", ignore=shutil.ignore_patterns("_ext", "_csrc", "__pycache__"))
+        subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "-w", str(tmp / "dist"), str(src)], check=True)
         wheel = next((tmp / "dist").glob("nanoep_b200-*.whl"))
         names = set(zipfile.ZipFile(wheel).namelist())
         for src in (ROOT / "csrc").rglob("*"):
