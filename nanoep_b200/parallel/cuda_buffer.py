@@ -327,6 +327,13 @@ class CudaBuffer:
         """Raise if a kernel of this buffer reported an error (timeouts, bad routing, ...)."""
         self._window.check_status()
 
+    def clear_status(self):
+        """Forget a reported device status (after the application has dealt with it) so later calls run
+        again.  Collective in spirit: a barrier timeout usually means the ranks' operation sequences have
+        diverged, so clear it on every rank and re-synchronise (for example with ``barrier()``) first."""
+        torch.cuda.synchronize(self._device)
+        self._window.clear_status(self._comm_stream.cuda_stream)
+
     def close(self):
         """Collectively drain, unmap peers, then free.  Idempotent; never call from ``__del__``."""
         if self._closed:

@@ -154,6 +154,15 @@ def test_bad_expert_id_reports_status():
         torch.cuda.synchronize()
         with pytest.raises(RuntimeError, match="expert id"):
             group.check_status()
+        # the status is sticky until cleared; afterwards the group works again
+        with pytest.raises(RuntimeError, match="expert id"):
+            group.dispatch([x], topk_idx=[idx.clamp(max=3)])
+        for w in group.windows:
+            w.clear_status(group.comm_stream.cuda_stream)
+        got = group.dispatch([x], topk_idx=[idx.clamp(max=3)])[0]
+        torch.cuda.synchronize()
+        group.check_status()
+        assert got.handle.layout.recv_count == 4
 
 
 def test_barrier_timeout_is_reported_not_fatal():
