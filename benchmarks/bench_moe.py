@@ -44,7 +44,6 @@ def parse_args():
     p.add_argument("--inter", type=int, default=2048)
     p.add_argument("--experts", type=int, default=256)
     p.add_argument("--topk", type=int, default=8)
-    p.add_argument("--comm-sms", type=int, default=32)
     p.add_argument("--gemm-only", action="store_true")
     p.add_argument("--arms", default="fused,fused_combine,unfused,nccl")
     return p.parse_args()

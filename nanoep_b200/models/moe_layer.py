@@ -47,7 +47,6 @@ class ExpertParallelMoE:
         self.fuse_combine = fuse_combine
         self.overlap_dispatch = overlap_dispatch
         self.device = w13.device
-        self.device_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.comm_ring_bytes = int(comm_ring_bytes)
         # tcgen05 cta_group::2 kernels (two SMs share each weight tile).  None = decide per call: a pair
         # needs two row blocks of the same expert, so with few blocks per expert the half-empty last

@@ -44,3 +44,10 @@ def test_fused_moe_layer_multi(tmp_path, nproc):
     assert code == 0, text[-4000:]
     for rank in range(nproc):
         assert f"NANOEP_MOE_LAYER_OK={rank}" in text, text[-4000:]
+
+
+def test_fused_moe_example(tmp_path):
+    nproc = 2 if _gpus() < 4 else 4
+    code, text = run_ranks("nanoep_b200.examples.fused_moe", nproc, log=tmp_path / "fused.log", cwd=ROOT, timeout=300)
+    assert code == 0, text[-4000:]
+    assert text.count("NANOEP_FUSED_MOE_OK=") == nproc, text[-4000:]

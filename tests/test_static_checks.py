@@ -45,3 +45,12 @@ def test_sm_budget_model():
     assert abs(p - (1 - math.comb(224, 8) / math.comb(256, 8))) < 1e-12
     assert sms.nvlink_gbs(("a",)) == 0.0
     assert sms.nvlink_gbs(("no-such-gpu-1", "no-such-gpu-2")) == 0.0  # nvidia-smi missing or GPUs unknown
+
+
+def test_nvtx_range_is_a_shared_noop_when_disabled():
+    from nanoep_b200.utils import tracing
+
+    if not tracing._ENABLED:
+        assert tracing.nvtx_range("a") is tracing.nvtx_range("b")
+    with tracing.nvtx_range("anything"):
+        pass
