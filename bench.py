@@ -56,96 +56,95 @@ def parse_args():
     return p.parse_args()
 
 
-class ClockSampler:
-    """Samples SM clocks, power and throttle reasons of one GPU while the timed region runs.
+_SAMPLER_CHILD = r"""
+import subprocess, sys, time
+target, period = sys.argv[1], float(sys.argv[2])
+try:
+    import pynvml as n
+    n.nvmlInit()
+    h = n.nvmlDeviceGetHandleByUUID(target if target.startswith("GPU-") else "GPU-" + target)
+    reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+    bits = [("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+            ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap")]
+    bits = [(name, int(getattr(n, attr))) for name, attr in bits if hasattr(n, attr)]
+    print("source nvml", flush=True)
+    while True:
+        mask = int(reasons(h))
+        active = ",".join(name for name, bit in bits if mask & bit) or "-"
+        print(time.time(), n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM), n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM), active, flush=True)
+        time.sleep(period)
+except Exception:
+    print("source nvidia-smi", flush=True)
+    query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    while True:
+        try:
+            out = subprocess.run(["nvidia-smi", "--query-gpu=" + query, "--format=csv,noheader,nounits", "-i", target],
+                                 capture_output=True, text=True, timeout=5).stdout.strip().splitlines()[0].split(",")
+            active = ",".join(nm for nm, flag in zip(names, out[2:6]) if flag.strip().lower().startswith("active")) or "-"
+            print(time.time(), float(out[0]), float(out[1]), active, flush=True)
+        except Exception:
+            pass
+        time.sleep(max(period, 0.2))
+"""
 
-    Uses NVML (read-only queries, a sample every few milliseconds) and falls back to ``nvidia-smi`` when
-    the Python bindings are missing.  Nothing is ever set or reset.
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU while the timed regions run.
+
+    The sampling loop lives in a child process (NVML queries, read-only; ``nvidia-smi`` as fallback) so that
+    it never competes with the benchmark's own thread for the interpreter; the parent only notes the
+    wall-clock windows of its timed regions and keeps the samples that fall inside them.  Nothing is ever
+    set or reset on the GPU.
     """
 
-    QUERY = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
-    )
-
-    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.02):
-        self.gpu_index = gpu_index
-        self.gpu_uuid = gpu_uuid
-        self.period_s = period_s
-        self.samples: list[tuple[float, float, list[str]]] = []  # (sm MHz, max MHz, active reasons)
-        self._stop = threading.Event()
-        self._thread = None
-        self._nvml = None
-        self._handle = None
+    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.005):
+        self.windows: list[list[float]] = []
+        self.source = None
+        target = gpu_uuid if gpu_uuid else str(gpu_index)
         try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            if gpu_uuid:
-                uuid = gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid
-                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
-            else:
-                self._handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
-            self._nvml = pynvml
-        except Exception:  # noqa: BLE001 - fall back to nvidia-smi
-            self._nvml = None
-
-    def _sample_nvml(self):
-        n = self._nvml
-        sm = float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
-        mx = float(n.nvmlDeviceGetMaxClockInfo(self._handle, n.NVML_CLOCK_SM))
-        mask = int(n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") else int(
-            n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
-        names = []
-        for name, attr in (("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
-                           ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap")):
-            bit = getattr(n, attr, None)
-            if bit is not None and mask & int(bit):
-                names.append(name)
-        self.samples.append((sm, mx, names))
-
-    def _sample_smi(self):
-        target = self.gpu_uuid if self.gpu_uuid else str(self.gpu_index)
-        out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", target],
-                             capture_output=True, text=True, timeout=5).stdout.strip()
-        if not out:
-            return
-        f = [v.strip() for v in out.splitlines()[0].split(",")]
-        names = [name for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8])
-                 if flag.lower().startswith("active")]
-        self.samples.append((float(f[1]), float(f[2]), names))
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                if self._nvml is not None:
-                    self._sample_nvml()
-                else:
-                    self._sample_smi()
-            except Exception:  # noqa: BLE001 - sampling is best effort
-                pass
-            self._stop.wait(self.period_s if self._nvml is not None else 0.2)
+            self._child = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, target, str(period_s)], stdout=subprocess.PIPE,
+                                           stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._child = None
 
     def __enter__(self):
-        self._stop.clear()  # re-enterable: samples of all timed regions accumulate
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
+        self.windows.append([time.time(), float("inf")])
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._thread.join(timeout=10)
+        self.windows[-1][1] = time.time()
 
     def summary(self) -> dict:
-        sm = [s[0] for s in self.samples]
-        mx = [s[1] for s in self.samples]
-        reasons = sorted({r for s in self.samples for r in s[2]})
+        lines = []
+        if self._child is not None:
+            self._child.terminate()  # this exact child only
+            try:
+                lines = self._child.communicate(timeout=10)[0].splitlines()
+            except subprocess.TimeoutExpired:
+                self._child.kill()
+            self._child = None
+        sm, mx, reasons = [], [], set()
+        for line in lines:
+            parts = line.split()
+            if parts[:1] == ["source"]:
+                self.source = parts[1]
+                continue
+            try:
+                ts, clock, top, active = float(parts[0]), float(parts[1]), float(parts[2]), parts[3]
+            except (ValueError, IndexError):
+                continue
+            if any(lo <= ts <= hi for lo, hi in self.windows):
+                sm.append(clock)
+                mx.append(top)
+                reasons.update(r for r in active.split(",") if r != "-")
         return {
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_max_mhz": max(mx) if mx else None,
-            "reasons": reasons,
+            "reasons": sorted(reasons),
             "samples": len(sm),
-            "source": "nvml" if self._nvml is not None else "nvidia-smi",
+            "source": self.source,
         }
 
 
@@ -196,6 +195,7 @@ def run_ours(args, rank, world, device, control_group):
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=control_group)
         return float(t.item())
 
+    clocks = ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid))  # child starts during warm-up
     with CudaBuffer(control_group, cfg, allow_multiple_reduction=args.multiple_reduction) as buf:
         state = {"handle": None}
 
@@ -231,7 +231,7 @@ def run_ours(args, rank, world, device, control_group):
             ext.take_phase_timings()
             ext.set_phase_timing(True)
         sync_all()
-        with ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid)) as clocks:
+        with clocks:
             wall0 = time.perf_counter()
             for i in range(args.steps):
                 xi = x_sets[i % len(x_sets)]
@@ -398,6 +398,7 @@ def run_nccl(args, rank, world, device, control_group):
         out.index_add_(0, token_of[order], returned.float())
         return out.to(x.dtype), mid, recv.shape[0]
 
+    clocks = ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid))
     for _ in range(args.warmup):
         dispatch_combine()
     torch.cuda.synchronize()
@@ -405,7 +406,7 @@ def run_nccl(args, rank, world, device, control_group):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     mids = []
-    with ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid)) as clocks:
+    with clocks:
         for i in range(args.steps):
             flush.fill_(i & 0xFF)
             starts[i].record()
