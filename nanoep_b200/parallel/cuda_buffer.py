@@ -12,6 +12,8 @@ Python exceptions from a status word instead of a device trap.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch.utils import deterministic
@@ -95,9 +97,15 @@ class CudaBuffer:
         config: EPConfig,
         *,
         allow_multiple_reduction: bool = False,
-        wait_timeout_s: float = 10.0,
-        mailbox_timeout_s: float = 60.0,
+        wait_timeout_s: float | None = None,
+        mailbox_timeout_s: float | None = None,
     ):
+        # Limits of the bounded waits: device side (peer barrier, bulk copies) and host side (N/C mailbox).
+        # Environment overrides: NANOEP_WAIT_TIMEOUT_S, NANOEP_MAILBOX_TIMEOUT_S.
+        if wait_timeout_s is None:
+            wait_timeout_s = float(os.environ.get("NANOEP_WAIT_TIMEOUT_S", "10"))
+        if mailbox_timeout_s is None:
+            mailbox_timeout_s = float(os.environ.get("NANOEP_MAILBOX_TIMEOUT_S", "60"))
         self._group = group
         self._config = config
         self._allow_multiple_reduction = allow_multiple_reduction
