@@ -39,7 +39,8 @@ __device__ __forceinline__ bool take_last_ticket(int* ticket) {
 // stage: copy this rank's tokens (x + gate weights) into its own window, snapshot and count the
 // routing, send the per-destination counts to the peers, peer barrier, derive N / C / offsets.
 // ------------------------------------------------------------------------------------------
-__device__ void stage_body(const StageParams& p) {
+// Returns true when the peer barrier succeeded (only meaningful to every block in fused mode).
+__device__ bool stage_body(const StageParams& p) {
     extern __shared__ int s_counts[];  // [R + E]
     const WindowLayout& L = p.c.layout;
     const int R = L.ranks, K = L.topk, H = L.hidden, Le = L.local_experts;
@@ -118,7 +119,29 @@ __device__ void stage_body(const StageParams& p) {
         for (int i = tid; i < R + E; i += blockDim.x)
             if (s_counts[i] != 0) atomicAdd(&count_acc[i], s_counts[i]);
     }
-    if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) return;
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
+        if (!p.fused) return false;
+        // Fused launch: wait (bounded) until the last block has run the peer barrier.  +epoch = go, -epoch = failed.
+        __shared__ int s_go;
+        if (tid == 0) {
+            const int want = int(p.epoch & 0x3fffffff) | 0x40000000;  // never zero
+            const uint64_t start = global_timer_ns();
+            int seen = 0;
+            for (;;) {
+                seen = ld_acquire_gpu(ctrl + WindowLayout::kGoWord);
+                if (seen == want || seen == -want) break;
+                __nanosleep(32);
+                if (global_timer_ns() - start > 2 * p.c.timeout_ns) {
+                    report(status, kBarrierTimeout, 0xffffu, kTagStage);
+                    seen = -want;
+                    break;
+                }
+            }
+            s_go = seen == want;
+        }
+        __syncthreads();
+        return s_go != 0;
+    }
 
     // ---- tail: one block per rank
     const int msg = int(L.msg_ints());
@@ -143,14 +166,22 @@ __device__ void stage_body(const StageParams& p) {
         if (lane == 0) s_ok = ok;
     }
     __syncthreads();
-    if (!p.fresh) return;
+    if (p.fused) {
+        if (tid == 0) {
+            const int want = int(p.epoch & 0x3fffffff) | 0x40000000;  // never zero
+            __threadfence();
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctrl + WindowLayout::kGoWord), "r"(s_ok ? want : -want) : "memory");
+        }
+        return s_ok != 0;
+    }
+    if (!p.fresh) return s_ok != 0;
     if (!s_ok) {
         if (tid == 0) {
             p.mailbox[1] = -2;
             p.mailbox[0] = -2;
             __threadfence_system();
         }
-        return;
+        return false;
     }
     const int* in = reinterpret_cast<const int*>(win + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride);
     __shared__ int s_total[2];
@@ -207,6 +238,7 @@ __device__ void stage_body(const StageParams& p) {
         p.mailbox[0] = s_total[0];
         __threadfence_system();
     }
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -910,13 +942,26 @@ __device__ void barrier_body(const BarrierParams& p) {
     __global__ void __launch_bounds__(threads) name##_kernel(const __grid_constant__ Params p) { name##_body(p); } \
     __global__ void __launch_bounds__(threads) name##_multi_kernel(const Params* all) { name##_body(all[blockIdx.y]); }
 
-NEP_KERNEL_PAIR(stage, StageParams, kStageThreads)
+__global__ void __launch_bounds__(kStageThreads) stage_kernel(const __grid_constant__ StageParams p) { stage_body(p); }
+__global__ void __launch_bounds__(kStageThreads) stage_multi_kernel(const StageParams* all) { stage_body(all[blockIdx.y]); }
 NEP_KERNEL_PAIR(plan, PlanParams, kPlanThreads)
 NEP_KERNEL_PAIR(pull, PullParams, 256)
 NEP_KERNEL_PAIR(push, PushParams, 256)
 NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
 NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
 NEP_KERNEL_PAIR(local_combine, LocalCombineParams, kReduceThreads)
+
+// stage + peer barrier + pull in one cooperative launch (cached dispatch, small calls)
+__global__ void __launch_bounds__(256) fused_cached_dispatch_kernel(const __grid_constant__ StageParams sp, const __grid_constant__ PullParams pp) {
+    if (!stage_body(sp)) return;
+    fence_proxy_async();
+    pull_body(pp);
+}
+__global__ void __launch_bounds__(256) fused_cached_dispatch_multi_kernel(const StageParams* sp, const PullParams* pp) {
+    if (!stage_body(sp[blockIdx.y])) return;
+    fence_proxy_async();
+    pull_body(pp[blockIdx.y]);
+}
 
 template <typename Params>
 cudaError_t launch_pair(void (*single)(const Params), void (*multi)(const Params*), const Params* params, LaunchShape shape, int threads,
@@ -988,6 +1033,21 @@ cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaS
     return launch_pair<BarrierParams>(barrier_kernel, barrier_multi_kernel, params, shape, 32, 0, stream);
 }
 
+cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
+                                         cudaStream_t stream) {
+    const bool multi = shape.ranks_y > 1;
+    const void* fn = multi ? (const void*)fused_cached_dispatch_multi_kernel : (const void*)fused_cached_dispatch_kernel;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+    }
+    const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
+    void* args_multi[2] = {(void*)&stage, (void*)&pull};
+    void* args_single[2] = {(void*)stage, (void*)pull};
+    // cooperative launch: fails instead of deadlocking if the grid cannot be resident at once
+    return cudaLaunchCooperativeKernel(fn, grid, dim3(warps * 32), multi ? args_multi : args_single, smem, stream);
+}
+
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream) {
     return launch_pair<LocalCombineParams>(local_combine_kernel, local_combine_multi_kernel, params, shape, kReduceThreads, 0, stream);
 }
@@ -1000,7 +1060,7 @@ int kernel_table(KernelInfo* out, int capacity) {
     const Entry entries[] = {
         {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
         {"push", (const void*)push_kernel},     {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
-        {"local_combine", (const void*)local_combine_kernel},
+        {"local_combine", (const void*)local_combine_kernel}, {"fused_cached_dispatch", (const void*)fused_cached_dispatch_kernel},
     };
     int n = 0;
     for (const Entry& e : entries) {

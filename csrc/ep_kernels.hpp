@@ -39,6 +39,7 @@ struct StageParams {
     int parity;
     int alignment;
     int skip_copy;  // single-rank groups: the pull reads x directly, nothing is staged
+    int fused;      // stage + pull in one launch: blocks wait for the barrier result instead of exiting
     uint64_t epoch;
     // handle tensors written by a fresh dispatch
     int64_t* snapshot;          // [T,K] copy of topk
@@ -145,6 +146,10 @@ cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, 
 cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
 cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream);
 cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaStream_t stream);
+// Cached dispatch for small calls: stage, peer barrier and pull in ONE cooperative launch (all blocks
+// resident; the block that finishes staging last runs the barrier and releases the others).
+cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
+                                         cudaStream_t stream);
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream);
 
 // Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.

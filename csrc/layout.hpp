@@ -56,7 +56,7 @@ struct WindowLayout {
     int64_t num_bytes;
 
     // ctrl sub-layout, in int32 units from ctrl_offset.
-    static constexpr int kTicketStage = 0, kTicketPush = 1, kCtrlHeaderInts = 16;
+    static constexpr int kTicketStage = 0, kTicketPush = 1, kGoWord = 2, kCtrlHeaderInts = 16;  // words 4..6: status
     NEP_HD int64_t ctrl_count_acc() const { return kCtrlHeaderInts; }                         // i32[R + E]
     NEP_HD int64_t ctrl_row_cursor() const { return ctrl_count_acc() + ranks + num_experts; }  // i32[R]
     NEP_HD int64_t ctrl_expert_cursor() const { return ctrl_row_cursor() + ranks; }            // i32[L]

@@ -16,11 +16,14 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
 #include <sstream>
 
 namespace nep {
 
 namespace {
+
+constexpr int kFusedDispatchDefaultTokens = 32;
 
 void cuda_check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
@@ -49,6 +52,16 @@ struct PhaseMarks {
     }
 };
 PhaseMarks g_marks;
+
+// Cached dispatches of at most this many tokens per rank use the single-launch path
+// (NANOEP_FUSED_DISPATCH_TOKENS overrides; 0 switches it off).
+int64_t fused_dispatch_max_tokens() {
+    static const int64_t value = [] {
+        const char* env = std::getenv("NANOEP_FUSED_DISPATCH_TOKENS");
+        return env != nullptr ? std::atoll(env) : int64_t(kFusedDispatchDefaultTokens);
+    }();
+    return value;
+}
 
 struct DeviceLimits {
     int sms;
@@ -279,17 +292,25 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             }
         }
     }
+    int64_t max_tokens_now = 0;
+    for (int i = 0; i < n; ++i) max_tokens_now = std::max<int64_t>(max_tokens_now, xs[i].size(0));
+    // Small cached calls: stage, peer barrier and pull go out as ONE cooperative launch.
+    bool gated = false;
+    for (const auto& t : tile_ready) gated = gated || t.has_value();
+    const bool fuse_small = !fresh && !gated && max_tokens_now <= fused_dispatch_max_tokens();
+    const StageParams* stage_dev = nullptr;
     {
         c10::cuda::CUDAStreamGuard on_comm(s.work);
-        const StageParams* dev = upload(stage, keep, cs);
+        for (int i = 0; i < n; ++i) stage[i].fused = fuse_small ? 1 : 0;
+        stage_dev = upload(stage, keep, cs);
         g_marks.mark("begin", cs);
-        PeerWindow::launches += 1;
-        int64_t max_tokens_now = 0;
-        for (int i = 0; i < n; ++i) max_tokens_now = std::max<int64_t>(max_tokens_now, xs[i].size(0));
-        // 16 warps per block, 4 row quarters per token: small calls get small grids
-        const int stage_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * num_sms, (max_tokens_now * 4 + 15) / 16)));
-        cuda_check(launch_stage(dev, LaunchShape{stage_grid, n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
-        g_marks.mark("stage", cs);
+        if (!fuse_small) {
+            PeerWindow::launches += 1;
+            // 16 warps per block, 4 row quarters per token: small calls get small grids
+            const int stage_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * num_sms, (max_tokens_now * 4 + 15) / 16)));
+            cuda_check(launch_stage(stage_dev, LaunchShape{stage_grid, n}, size_t(stage_smem_bytes(L)), cs), "stage launch");
+            g_marks.mark("stage", cs);
+        }
         if (fresh) {
             std::vector<PlanParams> plan(n);
             for (int i = 0; i < n; ++i) {
@@ -375,8 +396,18 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         int64_t max_items = 1;
         for (int i = 0; i < n; ++i) max_items = std::max<int64_t>(max_items, expand ? out.counts[i].second : out.counts[i].first * L.ranks);
         const int pull_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
-        cuda_check(launch_pull(dev, LaunchShape{pull_grid, n}, ring.warps, ring.smem_bytes, cs), "pull launch");
-        g_marks.mark("pull", cs);
+        if (fuse_small) {
+            // every block must be resident at once (one block per SM with this ring): bound the grid
+            const int64_t work = std::max<int64_t>(max_items, max_tokens_now * 4);
+            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), int64_t(32),
+                                                                               (work + ring.warps - 1) / ring.warps})));
+            cuda_check(launch_fused_cached_dispatch(stage_dev, dev, LaunchShape{fused_grid, n}, ring.warps, ring.smem_bytes, cs),
+                       "fused cached dispatch launch");
+            g_marks.mark("fused_dispatch", cs);
+        } else {
+            cuda_check(launch_pull(dev, LaunchShape{pull_grid, n}, ring.warps, ring.smem_bytes, cs), "pull launch");
+            g_marks.mark("pull", cs);
+        }
     }
     std::vector<at::Tensor> inputs, results;
     for (int i = 0; i < n; ++i) {
