@@ -25,7 +25,7 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
+import tempfile
 import time
 from datetime import timedelta
 
@@ -59,6 +59,7 @@ def parse_args():
 _SAMPLER_CHILD = r"""
 import subprocess, sys, time
 target, period = sys.argv[1], float(sys.argv[2])
+sys.stdout = open(sys.argv[3], "a", buffering=1)
 try:
     import pynvml as n
     n.nvmlInit()
@@ -102,12 +103,31 @@ class ClockSampler:
     def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.005):
         self.windows: list[list[float]] = []
         self.source = None
+        self.extended_s = 0.0
         target = gpu_uuid if gpu_uuid else str(gpu_index)
+        fd, self._path = tempfile.mkstemp(prefix="nanoep_clocks_", suffix=".txt")
+        os.close(fd)
         try:
-            self._child = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, target, str(period_s)], stdout=subprocess.PIPE,
-                                           stderr=subprocess.DEVNULL, text=True)
+            # samples go to a file, so that a long run can never block the child on a full pipe
+            self._child = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, target, str(period_s), self._path],
+                                           stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
         except OSError:
             self._child = None
+
+    def wait_ready(self, limit_s: float = 20.0) -> bool:
+        """Block (bounded) until the child has written its first sample, i.e. NVML is up."""
+        deadline = time.time() + limit_s
+        while self._child is not None and time.time() < deadline:
+            try:
+                with open(self._path) as f:
+                    if sum(1 for _ in f) >= 2:
+                        return True
+            except OSError:
+                pass
+            if self._child.poll() is not None:
+                return False
+            time.sleep(0.01)
+        return False
 
     def __enter__(self):
         self.windows.append([time.time(), float("inf")])
@@ -121,10 +141,16 @@ class ClockSampler:
         if self._child is not None:
             self._child.terminate()  # this exact child only
             try:
-                lines = self._child.communicate(timeout=10)[0].splitlines()
+                self._child.wait(timeout=10)
             except subprocess.TimeoutExpired:
                 self._child.kill()
             self._child = None
+        try:
+            with open(self._path) as f:
+                lines = f.read().splitlines()
+            os.unlink(self._path)
+        except OSError:
+            pass
         sm, mx, reasons = [], [], set()
         for line in lines:
             parts = line.split()
@@ -145,6 +171,8 @@ class ClockSampler:
             "reasons": sorted(reasons),
             "samples": len(sm),
             "source": self.source,
+            "window": "timed regions" + (f" + {self.extended_s:.2f} s of the same steps repeated untimed right after them"
+                                         if self.extended_s else ""),
         }
 
 
@@ -230,6 +258,7 @@ def run_ours(args, rank, world, device, control_group):
         if args.detail:
             ext.take_phase_timings()
             ext.set_phase_timing(True)
+        clocks.wait_ready()
         sync_all()
         with clocks:
             wall0 = time.perf_counter()
@@ -312,6 +341,19 @@ def run_ours(args, rank, world, device, control_group):
                 "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4,
             }
+        timed_wall_s = (ms_per_step + (e2e["ms_per_step"] if e2e else 0.0)) * 1e-3 * args.steps  # same value on every rank
+        if timed_wall_s < 0.25:
+            # The timed regions are shorter than a few sampling periods: repeat the same device-timed
+            # steps (not counted in any number) so that the clock record shows the GPU under this load.
+            extra = max(args.steps, int(0.3 / max(ms_per_step * 1e-3, 1e-6)))
+            sync_all()
+            t0 = time.time()
+            with clocks:
+                for i in range(extra):
+                    step(x_sets[i % len(x_sets)], idx, w)
+                sync_all()
+            clocks.extended_s = time.time() - t0
+            buf.check_status()
         clock_summary = clocks.summary()
 
     line = {
@@ -406,6 +448,7 @@ def run_nccl(args, rank, world, device, control_group):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     mids = []
+    clocks.wait_ready()
     with clocks:
         for i in range(args.steps):
             flush.fill_(i & 0xFF)

@@ -10,6 +10,14 @@ using nep::PeerWindow;
 
 namespace {
 
+// Routing metadata of one handle kept on the native side, so that cached dispatch and combine pass
+// one opaque object instead of converting eight tensors in and out of Python on every call.
+struct HandleState {
+    std::vector<at::Tensor> metadata;  // same order as DispatchOut::metadata
+    int64_t capacity;
+    bool expand;
+};
+
 py::dict layout_dict(const nep::WindowLayout& w) {
     py::dict d;
     d["signal_offset"] = w.signal_offset;
@@ -111,6 +119,41 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         },
         py::arg("windows"), py::arg("x"), py::arg("metadata"), py::arg("capacity"), py::arg("weights"), py::arg("bias"), py::arg("expand"),
         py::arg("allow_multiple_reduction"), py::arg("num_sms"), py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"));
+
+    py::class_<HandleState, std::shared_ptr<HandleState>>(m, "HandleState")
+        .def(py::init([](std::vector<at::Tensor> metadata, int64_t capacity, bool expand) {
+            return std::make_shared<HandleState>(HandleState{std::move(metadata), capacity, expand});
+        }))
+        .def_readonly("metadata", &HandleState::metadata)
+        .def_readonly("capacity", &HandleState::capacity)
+        .def_readonly("expand", &HandleState::expand);
+
+    // Single-rank fast paths (the list-based entry points above stay the general interface).
+    m.def(
+        "dispatch_cached",
+        [](PeerWindow& window, const at::Tensor& x, const c10::optional<at::Tensor>& weights, const std::shared_ptr<HandleState>& state,
+           bool zero_padding, int64_t num_sms, int64_t comm_stream, int64_t previous_event, bool async_op, double mailbox_timeout_s,
+           const c10::optional<at::Tensor>& tile_ready, int64_t ring_smem_limit) {
+            auto out = nep::dispatch({&window}, {x}, {c10::nullopt}, {weights}, {state->metadata}, {state->capacity}, 1, state->expand,
+                                     zero_padding, num_sms, comm_stream, previous_event, async_op, mailbox_timeout_s, {tile_ready},
+                                     ring_smem_limit);
+            auto& o = out.outputs[0];
+            return py::make_tuple(o[0], o[1], o[2], out.event);
+        },
+        py::arg("window"), py::arg("x"), py::arg("weights"), py::arg("state"), py::arg("zero_padding"), py::arg("num_sms"),
+        py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"), py::arg("mailbox_timeout_s") = 60.0,
+        py::arg("tile_ready") = c10::nullopt, py::arg("ring_smem_limit") = 0);
+    m.def(
+        "combine_single",
+        [](PeerWindow& window, const at::Tensor& x, const std::shared_ptr<HandleState>& state, const c10::optional<at::Tensor>& weights,
+           const c10::optional<at::Tensor>& bias, bool allow_multiple_reduction, int64_t num_sms, int64_t comm_stream, int64_t previous_event,
+           bool async_op) {
+            auto out = nep::combine({&window}, {x}, {state->metadata}, {state->capacity}, {weights}, {bias}, state->expand,
+                                    allow_multiple_reduction, num_sms, comm_stream, previous_event, async_op);
+            return py::make_tuple(out.outputs[0][0], out.outputs[0][1], out.event);
+        },
+        py::arg("window"), py::arg("x"), py::arg("state"), py::arg("weights"), py::arg("bias"), py::arg("allow_multiple_reduction"),
+        py::arg("num_sms"), py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"));
 
     m.def("combine_finish", &nep::combine_finish);
     m.def("next_combine_parity", [](PeerWindow& w) { return w.next_combine_parity(); });

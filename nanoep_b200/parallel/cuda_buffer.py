@@ -250,8 +250,19 @@ class CudaBuffer:
         if routing.shape != (x.shape[0], self._config.num_topk):
             raise ValueError("routing snapshot/topk_idx shape must match the buffer configuration")
 
-        cached_metadata, cached_capacity = ([], 0) if handle is None else (handle_metadata(handle), handle.layout.expanded_capacity)
         main_sms = self._resolve_num_sms(num_sms, handle)
+        if handle is not None and handle.native_state is not None:
+            with _OnDevice(self._device), nvtx_range("nanoep.dispatch.cached"):
+                out_x, out_idx, out_w, completed = self._backend.dispatch_cached(
+                    self._window, x, weights, handle.native_state, bool(zero_padding), main_sms, self._comm_stream.cuda_stream,
+                    -1 if previous_event is None else previous_event.cuda_event, bool(async_op), self._mailbox_timeout_s,
+                    tile_ready, int(ring_smem_limit),
+                )
+            event = CudaEvent(completed, keepalive=(self, x, routing, weights, handle)) if async_op else None
+            return NativeDispatchResult(
+                x=out_x, topk_idx=None if expand else out_idx, topk_weights=out_w if weights is not None else None, handle=handle, event=event
+            )
+        cached_metadata, cached_capacity = ([], 0) if handle is None else (handle_metadata(handle), handle.layout.expanded_capacity)
         with _OnDevice(self._device), nvtx_range("nanoep.dispatch.fresh" if handle is None else "nanoep.dispatch.cached"):
             outputs, metadata, counts, completed = self._backend.dispatch(
                 [self._window],
@@ -273,6 +284,7 @@ class CudaBuffer:
             )
         if handle is None:
             handle = build_handle(self, metadata[0], counts[0], expand, expert_alignment, x.dtype, main_sms)
+            handle.native_state = self._backend.HandleState(list(metadata[0]), int(counts[0][1]), bool(expand))
         event = CudaEvent(completed, keepalive=(self, x, routing, weights, handle)) if async_op else None
         out = outputs[0]
         return NativeDispatchResult(
@@ -305,6 +317,14 @@ class CudaBuffer:
             raise ValueError("combine handle configuration does not match this CudaBuffer")
         validate_combine_inputs(self._config, handle, x, weights, bias, torch.device("cuda", self._device))
         main_sms = self._resolve_num_sms(num_sms, handle)
+        if handle.native_state is not None:
+            with _OnDevice(self._device), nvtx_range("nanoep.combine"):
+                out_x, out_w, completed = self._backend.combine_single(
+                    self._window, x, handle.native_state, weights, bias, self._allow_multiple_reduction, main_sms,
+                    self._comm_stream.cuda_stream, -1 if previous_event is None else previous_event.cuda_event, bool(async_op),
+                )
+            event = CudaEvent(completed, keepalive=(self, x, handle, weights, bias)) if async_op else None
+            return NativeCombineResult(x=out_x, topk_weights=out_w if weights is not None else None, event=event)
         with _OnDevice(self._device), nvtx_range("nanoep.combine"):
             outputs, completed = self._backend.combine(
                 [self._window],

@@ -62,6 +62,8 @@ class NativeHandle:
     num_sms: int | None = None
     # expanded layout: int32 [C], slot -> receive_row * K + k, -1 for padding; empty for compact
     slot_map: torch.Tensor | None = None
+    # native-side copy of the metadata (CUDA backend): lets cached dispatch and combine pass one object
+    native_state: Any = None
 
     @property
     def local_topk_idx(self) -> torch.Tensor:

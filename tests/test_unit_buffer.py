@@ -190,6 +190,18 @@ class FakeBackend:
         self.calls.append(("combine", args))
         return [[torch.zeros(5, 256, dtype=torch.bfloat16), torch.zeros(5, 2)]], "EVENT" if args[11] else None
 
+    @staticmethod
+    def HandleState(metadata, capacity, expand):
+        return SimpleNamespace(metadata=metadata, capacity=capacity, expand=expand)
+
+    def dispatch_cached(self, *args):
+        self.calls.append(("dispatch_cached", args))
+        return torch.zeros(4, 256, dtype=torch.bfloat16), torch.zeros(0, dtype=torch.int64), torch.zeros(4), "EVENT" if args[8] else None
+
+    def combine_single(self, *args):
+        self.calls.append(("combine_single", args))
+        return torch.zeros(5, 256, dtype=torch.bfloat16), torch.zeros(5, 2), "EVENT" if args[9] else None
+
 
 def make_buffer(monkeypatch):
     buf = CudaBuffer.__new__(CudaBuffer)
@@ -223,14 +235,23 @@ def test_dispatch_argument_forwarding_and_handles(monkeypatch):
     assert a[6:13] == (16, True, True, 12, 77, 1234, True)
     assert got2.topk_idx is None and got2.topk_weights is None and got2.event.event == "EVENT"
     assert got2.event.keepalive[0] is buf and got2.event.keepalive[1] is x
-    # cached: same handle object, metadata forwarded in the fixed order, budget inherited
-    again = buf.dispatch(x, handle=got2.handle, weights=w)
-    a = buf._backend.calls[-1][1]
-    assert again.handle is got2.handle and a[2] == [None] and a[9] == 12 and a[7] is True and a[6] == 16
+    # cached: same handle object; the native state made by the fresh call carries the metadata in the fixed order
     h = got2.handle
     expect = [h.layout.recv_metadata, h.layout.expert_counts, h.layout.expert_offsets, h.dst_slots, h.send_counts, h.topk_idx,
               h.layout.recv_rank_prefix, h.slot_map]
+    st = h.native_state
+    assert all(u is v for u, v in zip(st.metadata, expect)) and st.capacity == 4 and st.expand is True
+    again = buf.dispatch(x, handle=h, weights=w, zero_padding=True, async_op=True)
+    name, a = buf._backend.calls[-1]
+    assert name == "dispatch_cached" and again.handle is h and again.topk_idx is None and again.event.event == "EVENT"
+    assert a[:3] == ("WINDOW", x, w) and a[3] is st and a[4:10] == (True, 12, 77, -1, True, 60.0) and a[10] is None and a[11] == 0
+    # a handle without native state (built by hand) takes the list interface: budget and layout inherited
+    h.native_state = None
+    again = buf.dispatch(x, handle=h, weights=w)
+    name, a = buf._backend.calls[-1]
+    assert name == "dispatch" and again.handle is h and a[2] == [None] and a[9] == 12 and a[7] is True and a[6] == 16
     assert all(u is v for u, v in zip(a[4][0], expect)) and a[5] == [4]
+    h.native_state = st
     # num_sms = 0 -> model (no NVLink information in this process -> all SMs)
     buf.dispatch(x, topk_idx=idx, num_sms=0)
     assert buf._backend.calls[-1][1][9] == 78
@@ -263,6 +284,12 @@ def test_combine_argument_forwarding(monkeypatch):
     assert name == "combine" and a[0] == ["WINDOW"] and a[1][0] is y and a[3] == [4] and a[5] == [None]
     assert a[6:12] == (True, False, 20, 77, -1, True)
     assert out.topk_weights is not None and out.event.keepalive[2] is handle
+    handle.native_state = st = FakeBackend.HandleState([], 4, True)
+    wts, bias = torch.zeros(4), torch.zeros(5, 256, dtype=torch.bfloat16)
+    out = buf.combine(y, handle, weights=wts, bias=bias, async_op=True)
+    name, a = buf._backend.calls[-1]
+    assert name == "combine_single" and a == ("WINDOW", y, st, wts, bias, False, 20, 77, -1, True)
+    assert out.topk_weights is not None and out.event.event == "EVENT" and out.event.keepalive[2] is handle
     other = make_buffer(monkeypatch)
     with pytest.raises(ValueError, match="another"):
         other.combine(y, handle)
