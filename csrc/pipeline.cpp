@@ -157,9 +157,16 @@ Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bo
     }
     if (previous_event != -1)
         cuda_check(cudaStreamWaitEvent(compute.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
-    cudaEvent_t tail = handover_event(1);
-    cuda_check(cudaEventRecord(tail, comm.stream()), "record comm stream");
-    cuda_check(cudaStreamWaitEvent(compute.stream(), tail, 0), "wait comm stream");
+    // An idle communication stream (the usual case for synchronous callers) needs no hand-over.
+    const cudaError_t busy = cudaStreamQuery(comm.stream());
+    if (busy == cudaErrorNotReady) {
+        (void)cudaGetLastError();  // "not ready" is an answer, not an error to keep
+        cudaEvent_t tail = handover_event(1);
+        cuda_check(cudaEventRecord(tail, comm.stream()), "record comm stream");
+        cuda_check(cudaStreamWaitEvent(compute.stream(), tail, 0), "wait comm stream");
+    } else {
+        cuda_check(busy, "query comm stream");
+    }
     return Streams{compute, comm, compute};
 }
 

@@ -28,7 +28,7 @@ def main():
         # build from a copy so that no build/ or egg-info directory appears in the checkout
         src = tmp / "src"
         src.mkdir()
-        for name in ("pyproject.toml", "setup.py", "MANIFEST.in", "README.md", "DESIGN.md"):
+        for name in ("pyproject.toml", "setup.py", "MANIFEST.in", "README.md"):
             shutil.copy(ROOT / name, src / name)
         shutil.copytree(ROOT / "csrc", src / "csrc")
         shutil.copytree(ROOT / "nanoep_b200", src / "nanoep_b200", ignore=shutil.ignore_patterns("_ext", "_csrc", "__pycache__"))
