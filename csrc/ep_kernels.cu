@@ -1038,8 +1038,16 @@ cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullPar
     const bool multi = shape.ranks_y > 1;
     const void* fn = multi ? (const void*)fused_cached_dispatch_multi_kernel : (const void*)fused_cached_dispatch_kernel;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
+        // as in launch_pair: raise the limit once per (kernel, device), and only when it grows
+        static thread_local size_t granted[2][64] = {};
+        int device = 0;
+        cudaGetDevice(&device);
+        size_t& have = granted[multi ? 1 : 0][device & 63];
+        if (smem > have) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return e;
+            have = smem;
+        }
     }
     const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
     void* args_multi[2] = {(void*)&stage, (void*)&pull};
