@@ -36,6 +36,9 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", choices=("ours", "nccl"), default="ours")
     p.add_argument("--tokens", type=str, default="1,8,32,128,512,4096")
+    p.add_argument("--fused", type=str, default="",
+                   help="decode/published: comma-separated dispatch_tokens:combine_tokens:blocks settings of the single-launch paths to "
+                        "measure one after the other (empty: the library defaults)")
     return p.parse_args()
 
 
@@ -117,8 +120,13 @@ def main():
             sizes = [int(t) for t in args.tokens.split(",")]
             if args.config == "published":
                 H, sizes = 4096, [256]
+            from nanoep_b200.utils.build import load_extension
+
+            ext = load_extension()
+            settings = [tuple(int(v) for v in item.split(":")) for item in args.fused.split(",") if item] or [ext.fused_limits()]
             with CudaBuffer(control, EPConfig(E, K, H, max(sizes))) as buf:
-                for T in sizes:
+                for setting, T in ((s_, t_) for s_ in settings for t_ in sizes):
+                    ext.set_fused_limits(*setting)
                     idx, w = uniform_routing(T, E, K, seed=3 + rank)
                     x = torch.randn(T, H, generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16).to(device)
                     idx, w = idx.to(device), w.to(device)
@@ -172,7 +180,8 @@ def main():
                             host_cached.append((h1 - h0) * 1e3)
                             host_comb.append((h3 - h2) * 1e3)
                     buf.check_status()
-                    rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H}
+                    rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H,
+                           "single_launch_limits": dict(zip(("dispatch_tokens", "combine_tokens", "blocks"), ext.fused_limits()))}
                     if args.config == "published":
                         # reference figure (single-node H20): NanoEP / DeepEP 2.1.0 microseconds
                         published = {2: (69.4, 40.2, 51.9), 4: (78.5, 54.9, 70.4), 8: (147.1, 91.8, 102.5)}.get(world)

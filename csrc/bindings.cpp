@@ -158,6 +158,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("combine_finish", &nep::combine_finish);
     m.def("next_combine_parity", [](PeerWindow& w) { return w.next_combine_parity(); });
     m.def("group_barrier", &nep::group_barrier);
+    m.def("fused_limits", [] {
+        const nep::FusedLimits f = nep::fused_limits();
+        return py::make_tuple(f.dispatch_tokens, f.combine_tokens, f.blocks);
+    });
+    m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("combine_tokens") = -1, py::arg("blocks") = -1);
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });

@@ -35,6 +35,39 @@ __device__ __forceinline__ bool take_last_ticket(int* ticket) {
     return last != 0;
 }
 
+// Single-launch paths: the block that took the last ticket runs the peer barrier and then tells the other
+// blocks of its rank the outcome through one word: +tag = go, -tag = failed (tag derives from the epoch, never 0).
+__device__ __forceinline__ int go_tag(uint64_t epoch) { return int(epoch & 0x3fffffff) | 0x40000000; }
+
+__device__ __forceinline__ void publish_go(int* ctrl, uint64_t epoch, bool ok) {
+    const int want = go_tag(epoch);
+    __threadfence();
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctrl + WindowLayout::kGoWord), "r"(ok ? want : -want) : "memory");
+}
+
+// Called by every thread of a block; thread 0 polls (bounded), the block gets the outcome.
+__device__ bool wait_go(int* ctrl, uint64_t epoch, uint64_t timeout_ns, StatusRef status, uint32_t tag) {
+    __shared__ int s_go;
+    if (threadIdx.x == 0) {
+        const int want = go_tag(epoch);
+        const uint64_t start = global_timer_ns();
+        int seen = 0;
+        for (;;) {
+            seen = ld_acquire_gpu(ctrl + WindowLayout::kGoWord);
+            if (seen == want || seen == -want) break;
+            __nanosleep(32);
+            if (global_timer_ns() - start > 2 * timeout_ns) {
+                report(status, kBarrierTimeout, 0xffffu, tag);
+                seen = -want;
+                break;
+            }
+        }
+        s_go = seen == want;
+    }
+    __syncthreads();
+    return s_go != 0;
+}
+
 // ------------------------------------------------------------------------------------------
 // stage: copy this rank's tokens (x + gate weights) into its own window, snapshot and count the
 // routing, send the per-destination counts to the peers, peer barrier, derive N / C / offsets.
@@ -121,26 +154,7 @@ __device__ bool stage_body(const StageParams& p) {
     }
     if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
         if (!p.fused) return false;
-        // Fused launch: wait (bounded) until the last block has run the peer barrier.  +epoch = go, -epoch = failed.
-        __shared__ int s_go;
-        if (tid == 0) {
-            const int want = int(p.epoch & 0x3fffffff) | 0x40000000;  // never zero
-            const uint64_t start = global_timer_ns();
-            int seen = 0;
-            for (;;) {
-                seen = ld_acquire_gpu(ctrl + WindowLayout::kGoWord);
-                if (seen == want || seen == -want) break;
-                __nanosleep(32);
-                if (global_timer_ns() - start > 2 * p.c.timeout_ns) {
-                    report(status, kBarrierTimeout, 0xffffu, kTagStage);
-                    seen = -want;
-                    break;
-                }
-            }
-            s_go = seen == want;
-        }
-        __syncthreads();
-        return s_go != 0;
+        return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
     }
 
     // ---- tail: one block per rank
@@ -167,11 +181,7 @@ __device__ bool stage_body(const StageParams& p) {
     }
     __syncthreads();
     if (p.fused) {
-        if (tid == 0) {
-            const int want = int(p.epoch & 0x3fffffff) | 0x40000000;  // never zero
-            __threadfence();
-            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctrl + WindowLayout::kGoWord), "r"(s_ok ? want : -want) : "memory");
-        }
+        if (tid == 0) publish_go(ctrl, p.epoch, s_ok != 0);
         return s_ok != 0;
     }
     if (!p.fresh) return s_ok != 0;
@@ -611,7 +621,8 @@ __device__ __forceinline__ int4 pack8(const float* acc) {
     return v;
 }
 
-__device__ void push_body(const PushParams& p) {
+// Returns true when the peer barrier succeeded (only meaningful to every block in fused mode).
+__device__ bool push_body(const PushParams& p) {
     extern __shared__ __align__(128) char s_ring[];
     const WindowLayout& L = p.c.layout;
     const int R = L.ranks, K = L.topk, H = L.hidden;
@@ -763,11 +774,21 @@ __device__ void push_body(const PushParams& p) {
     }
     bulk_wait<0>();
     __threadfence_system();
-    if (!take_last_ticket(ctrl + WindowLayout::kTicketPush)) return;
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketPush)) {
+        if (!p.fused) return false;
+        return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagPush);
+    }
     if (threadIdx.x == 0) ctrl[WindowLayout::kTicketPush] = 0;
     __threadfence_system();
     __syncthreads();
-    if (warp == 0) peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagPush);
+    __shared__ int s_ok;
+    if (warp == 0) {
+        const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagPush);
+        if (lane == 0) s_ok = ok;
+    }
+    __syncthreads();
+    if (p.fused && threadIdx.x == 0) publish_go(ctrl, p.epoch, s_ok != 0);
+    return s_ok != 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -946,7 +967,8 @@ __global__ void __launch_bounds__(kStageThreads) stage_kernel(const __grid_const
 __global__ void __launch_bounds__(kStageThreads) stage_multi_kernel(const StageParams* all) { stage_body(all[blockIdx.y]); }
 NEP_KERNEL_PAIR(plan, PlanParams, kPlanThreads)
 NEP_KERNEL_PAIR(pull, PullParams, 256)
-NEP_KERNEL_PAIR(push, PushParams, 256)
+__global__ void __launch_bounds__(256) push_kernel(const __grid_constant__ PushParams p) { push_body(p); }
+__global__ void __launch_bounds__(256) push_multi_kernel(const PushParams* all) { push_body(all[blockIdx.y]); }
 NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
 NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
 NEP_KERNEL_PAIR(local_combine, LocalCombineParams, kReduceThreads)
@@ -961,6 +983,16 @@ __global__ void __launch_bounds__(256) fused_cached_dispatch_multi_kernel(const 
     if (!stage_body(sp[blockIdx.y])) return;
     fence_proxy_async();
     pull_body(pp[blockIdx.y]);
+}
+
+// push + peer barrier + reduce in one cooperative launch (small combines)
+__global__ void __launch_bounds__(256) fused_combine_kernel(const __grid_constant__ PushParams pp, const __grid_constant__ ReduceParams rp) {
+    if (!push_body(pp)) return;
+    reduce_body(rp);
+}
+__global__ void __launch_bounds__(256) fused_combine_multi_kernel(const PushParams* pp, const ReduceParams* rp) {
+    if (!push_body(pp[blockIdx.y])) return;
+    reduce_body(rp[blockIdx.y]);
 }
 
 template <typename Params>
@@ -1033,13 +1065,14 @@ cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaS
     return launch_pair<BarrierParams>(barrier_kernel, barrier_multi_kernel, params, shape, 32, 0, stream);
 }
 
-cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
-                                         cudaStream_t stream) {
+namespace {
+// Cooperative launch of a two-parameter-block kernel: fails instead of deadlocking if the grid cannot be resident at once.
+cudaError_t launch_cooperative(const void* single, const void* multi_fn, const void* first, const void* second, LaunchShape shape, int warps,
+                               size_t smem, cudaStream_t stream, size_t (*granted)[64]) {
     const bool multi = shape.ranks_y > 1;
-    const void* fn = multi ? (const void*)fused_cached_dispatch_multi_kernel : (const void*)fused_cached_dispatch_kernel;
+    const void* fn = multi ? multi_fn : single;
     if (smem > 48 * 1024) {
         // as in launch_pair: raise the limit once per (kernel, device), and only when it grows
-        static thread_local size_t granted[2][64] = {};
         int device = 0;
         cudaGetDevice(&device);
         size_t& have = granted[multi ? 1 : 0][device & 63];
@@ -1050,10 +1083,25 @@ cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullPar
         }
     }
     const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
-    void* args_multi[2] = {(void*)&stage, (void*)&pull};
-    void* args_single[2] = {(void*)stage, (void*)pull};
-    // cooperative launch: fails instead of deadlocking if the grid cannot be resident at once
+    // multi: the kernel takes the two device arrays; single: the two blocks by value
+    void* args_multi[2] = {(void*)&first, (void*)&second};
+    void* args_single[2] = {(void*)first, (void*)second};
     return cudaLaunchCooperativeKernel(fn, grid, dim3(warps * 32), multi ? args_multi : args_single, smem, stream);
+}
+}  // namespace
+
+cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
+                                         cudaStream_t stream) {
+    static thread_local size_t granted[2][64] = {};
+    return launch_cooperative((const void*)fused_cached_dispatch_kernel, (const void*)fused_cached_dispatch_multi_kernel, stage, pull, shape,
+                              warps, smem, stream, granted);
+}
+
+cudaError_t launch_fused_combine(const PushParams* push, const ReduceParams* reduce, LaunchShape shape, int warps, size_t smem,
+                                 cudaStream_t stream) {
+    static thread_local size_t granted[2][64] = {};
+    return launch_cooperative((const void*)fused_combine_kernel, (const void*)fused_combine_multi_kernel, push, reduce, shape, warps, smem,
+                              stream, granted);
 }
 
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream) {
@@ -1069,6 +1117,7 @@ int kernel_table(KernelInfo* out, int capacity) {
         {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
         {"push", (const void*)push_kernel},     {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
         {"local_combine", (const void*)local_combine_kernel}, {"fused_cached_dispatch", (const void*)fused_cached_dispatch_kernel},
+        {"fused_combine", (const void*)fused_combine_kernel},
     };
     int n = 0;
     for (const Entry& e : entries) {

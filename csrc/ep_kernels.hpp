@@ -98,6 +98,7 @@ struct PushParams {
     int mode;
     int parity;
     int stages;
+    int fused;               // 1: every block waits for the peer barrier's outcome (single-launch combine)
     uint64_t epoch;
 };
 
@@ -150,6 +151,9 @@ cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaS
 // resident; the block that finishes staging last runs the barrier and releases the others).
 cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
                                          cudaStream_t stream);
+// push + peer barrier + reduce in one cooperative launch (small combines)
+cudaError_t launch_fused_combine(const PushParams* push, const ReduceParams* reduce, LaunchShape shape, int warps, size_t smem,
+                                 cudaStream_t stream);
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream);
 
 // Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.

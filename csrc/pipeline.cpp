@@ -16,6 +16,8 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
+#include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <sstream>
 
@@ -24,6 +26,8 @@ namespace nep {
 namespace {
 
 constexpr int kFusedDispatchDefaultTokens = 32;
+constexpr int kFusedDefaultBlocks = 32;
+constexpr int kFusedCombineDefaultTokens = 32;
 
 void cuda_check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
@@ -53,15 +57,31 @@ struct PhaseMarks {
 };
 PhaseMarks g_marks;
 
-// Cached dispatches of at most this many tokens per rank use the single-launch path
-// (NANOEP_FUSED_DISPATCH_TOKENS overrides; 0 switches it off).
-int64_t fused_dispatch_max_tokens() {
-    static const int64_t value = [] {
-        const char* env = std::getenv("NANOEP_FUSED_DISPATCH_TOKENS");
-        return env != nullptr ? std::atoll(env) : int64_t(kFusedDispatchDefaultTokens);
-    }();
-    return value;
+// Single-launch paths for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
+// stage, peer barrier and pull as one cooperative launch; combines whose ranks contributed at most
+// `combine_tokens` source tokens run push, peer barrier and reduce as one.  `blocks` bounds their grids
+// (every block must be resident at once and spins on one word while the last block runs the peer
+// barrier).  Defaults come from NANOEP_FUSED_DISPATCH_TOKENS / NANOEP_FUSED_COMBINE_TOKENS /
+// NANOEP_FUSED_BLOCKS (0 tokens switches a path off) and can be changed at run time.
+struct FusedLimitsState {
+    std::atomic<int64_t> dispatch_tokens, combine_tokens, blocks;
+    FusedLimitsState() {
+        auto read = [](const char* name, int64_t fallback) {
+            const char* env = std::getenv(name);
+            return env != nullptr ? std::atoll(env) : fallback;
+        };
+        dispatch_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_DISPATCH_TOKENS", kFusedDispatchDefaultTokens));
+        combine_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_COMBINE_TOKENS", kFusedCombineDefaultTokens));
+        blocks = std::max<int64_t>(1, read("NANOEP_FUSED_BLOCKS", kFusedDefaultBlocks));
+    }
+};
+FusedLimitsState& fused_state() {
+    static FusedLimitsState state;
+    return state;
 }
+int64_t fused_dispatch_max_tokens() { return fused_state().dispatch_tokens.load(std::memory_order_relaxed); }
+int64_t fused_combine_max_tokens() { return fused_state().combine_tokens.load(std::memory_order_relaxed); }
+int64_t fused_max_blocks() { return fused_state().blocks.load(std::memory_order_relaxed); }
 
 struct DeviceLimits {
     int sms;
@@ -406,7 +426,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         if (fuse_small) {
             // every block must be resident at once (one block per SM with this ring): bound the grid
             const int64_t work = std::max<int64_t>(max_items, max_tokens_now * 4);
-            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), int64_t(32),
+            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), fused_max_blocks(),
                                                                                (work + ring.warps - 1) / ring.warps})));
             cuda_check(launch_fused_cached_dispatch(stage_dev, dev, LaunchShape{fused_grid, n}, ring.warps, ring.smem_bytes, cs),
                        "fused cached dispatch launch");
@@ -561,22 +581,34 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     }
     {
         c10::cuda::CUDAStreamGuard on_comm(s.work);
-        const PushParams* pdev = upload(push, keep, cs);
-        g_marks.mark("begin", cs);
-        PeerWindow::launches += 1;
         int64_t max_items = 1, max_tokens_now = 1;
         for (int i = 0; i < n; ++i) {
             max_items = std::max<int64_t>(max_items, expand ? capacity[i] : meta[i][0].size(0) * L.ranks);
             max_tokens_now = std::max<int64_t>(max_tokens_now, meta[i][5].size(0));
         }
-        const int push_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
-        cuda_check(launch_push(pdev, LaunchShape{push_grid, n}, ring.warps, ring.smem_bytes, cs), "push launch");
-        g_marks.mark("push", cs);
+        // Small combines: push, peer barrier and reduce go out as ONE cooperative launch.
+        const bool fuse_small = max_tokens_now <= fused_combine_max_tokens();
+        for (int i = 0; i < n; ++i) push[i].fused = fuse_small ? 1 : 0;
+        const PushParams* pdev = upload(push, keep, cs);
         const ReduceParams* rdev = upload(reduce, keep, cs);
+        g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
-        const int reduce_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * lim.sms, (max_tokens_now + 15) / 16)));
-        cuda_check(launch_reduce(rdev, LaunchShape{reduce_grid, n}, cs), "reduce launch");
-        g_marks.mark("reduce", cs);
+        if (fuse_small) {
+            // every block must be resident at once (one block per SM with this ring): bound the grid
+            const int64_t work = std::max<int64_t>(max_items, max_tokens_now);
+            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), fused_max_blocks(),
+                                                                               (work + ring.warps - 1) / ring.warps})));
+            cuda_check(launch_fused_combine(pdev, rdev, LaunchShape{fused_grid, n}, ring.warps, ring.smem_bytes, cs), "fused combine launch");
+            g_marks.mark("fused_combine", cs);
+        } else {
+            const int push_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
+            cuda_check(launch_push(pdev, LaunchShape{push_grid, n}, ring.warps, ring.smem_bytes, cs), "push launch");
+            g_marks.mark("push", cs);
+            PeerWindow::launches += 1;
+            const int reduce_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * lim.sms, (max_tokens_now + 15) / 16)));
+            cuda_check(launch_reduce(rdev, LaunchShape{reduce_grid, n}, cs), "reduce launch");
+            g_marks.mark("reduce", cs);
+        }
     }
     std::vector<at::Tensor> inputs, results;
     for (int i = 0; i < n; ++i) {
@@ -634,6 +666,14 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
     PeerWindow::launches += 1;
     cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
     return outs;
+}
+
+FusedLimits fused_limits() { return FusedLimits{fused_dispatch_max_tokens(), fused_combine_max_tokens(), fused_max_blocks()}; }
+
+void set_fused_limits(int64_t dispatch_tokens, int64_t combine_tokens, int64_t blocks) {
+    if (dispatch_tokens >= 0) fused_state().dispatch_tokens = dispatch_tokens;
+    if (combine_tokens >= 0) fused_state().combine_tokens = combine_tokens;
+    if (blocks >= 1) fused_state().blocks = blocks;
 }
 
 void set_phase_timing(bool enabled) { g_marks.enabled = enabled; }

@@ -56,6 +56,14 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
                                        const std::vector<int64_t>& parity, const std::vector<c10::optional<at::Tensor>>& bias);
 
 // Per-phase device times (name, microseconds) of the operations issued since the last call.
+// Token thresholds and grid bound of the single-launch paths for small calls (see pipeline.cpp).
+struct FusedLimits {
+    int64_t dispatch_tokens, combine_tokens, blocks;
+};
+FusedLimits fused_limits();
+// Negative token values / blocks < 1 leave the respective setting unchanged.
+void set_fused_limits(int64_t dispatch_tokens, int64_t combine_tokens, int64_t blocks);
+
 void set_phase_timing(bool enabled);
 std::vector<std::pair<std::string, double>> take_phase_timings();
 

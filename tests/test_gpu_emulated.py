@@ -14,6 +14,21 @@ from nanoep_b200.testing.checks import assert_dispatch_matches, source_reference
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["split_launches", "single_launch"])
+def launch_path(request):
+    """Run a test once with the small-call single-launch kernels switched off and once with them forced on."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    before = ext.fused_limits()
+    if request.param == "single_launch":
+        ext.set_fused_limits(dispatch_tokens=1 << 20, combine_tokens=1 << 20)
+    else:
+        ext.set_fused_limits(dispatch_tokens=0, combine_tokens=0)
+    yield request.param
+    ext.set_fused_limits(*before)
+
+
 def _to_cuda(ts):
     return [t.cuda() for t in ts]
 
@@ -66,7 +81,7 @@ def test_dispatch_layouts(world, kind):
 
 
 @pytest.mark.parametrize("world,multiple", [(1, False), (2, False), (2, True), (8, False), (8, True)])
-def test_combine_modes_bit_exact(world, multiple):
+def test_combine_modes_bit_exact(world, multiple, launch_path):
     for kind in ("mixed", "masked", "empty", "skew"):
         case = make_case(world, kind=kind, seed=9, hidden=512, tokens=9)
         cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
@@ -91,7 +106,7 @@ def test_combine_modes_bit_exact(world, multiple):
                         torch.testing.assert_close(back[r].topk_weights.cpu(), want_w, rtol=0, atol=0)
 
 
-def test_cached_replay_and_poison():
+def test_cached_replay_and_poison(launch_path):
     world = 4
     case = make_case(world, kind="random", seed=21, hidden=256, tokens=13)
     cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
