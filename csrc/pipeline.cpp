@@ -25,9 +25,9 @@ namespace nep {
 
 namespace {
 
-constexpr int kFusedDispatchDefaultTokens = 32;
-constexpr int kFusedDefaultBlocks = 32;
-constexpr int kFusedCombineDefaultTokens = 32;
+constexpr int kFusedDispatchDefaultTokens = 64;
+constexpr int kFusedDefaultBlocks = 1024;  // i.e. bounded by the SM budget and co-residency only
+constexpr int kFusedCombineDefaultTokens = 512;
 
 void cuda_check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {

@@ -103,23 +103,24 @@ def lifetime(group, rank, world, multiple):
             assert_dispatch_matches(again, xs2, case.indices, case.weights, case.num_experts, rank,
                                     expand=True, alignment=4, zero_padding=True)
             checks += 1
-        # the same round trips through the single-launch kernels for small calls (forced on for these sizes)
+        # the same round trips with the single-launch kernels for small calls forced on, then switched off
         from nanoep_b200.utils.build import load_extension
 
         ext = load_extension()
         before = ext.fused_limits()
-        ext.set_fused_limits(dispatch_tokens=1 << 20, combine_tokens=1 << 20)
         try:
-            for kind in ("random", "masked"):
-                case = make_case(world, kind=kind, seed=31, hidden=512, tokens=37)
-                for expand in (False, True):
-                    alignment = 4 if expand else 1
-                    got = check_round_trip(buf, case, rank, world, expand, alignment, multiple, async_op=False, delayed=(kind == "random"))
-                    again = buf.dispatch(case.xs[rank].cuda(), handle=got.handle, weights=case.weights[rank].cuda(), zero_padding=True)
-                    torch.cuda.synchronize()
-                    assert_dispatch_matches(again, case.xs, case.indices, case.weights, case.num_experts, rank,
-                                            expand=expand, alignment=alignment, zero_padding=True)
-                    checks += 1
+            for limit in (1 << 20, 0):
+                ext.set_fused_limits(dispatch_tokens=limit, combine_tokens=limit)
+                for kind in ("random", "masked"):
+                    case = make_case(world, kind=kind, seed=31, hidden=512, tokens=37)
+                    for expand in (False, True):
+                        alignment = 4 if expand else 1
+                        got = check_round_trip(buf, case, rank, world, expand, alignment, multiple, async_op=False, delayed=(kind == "random"))
+                        again = buf.dispatch(case.xs[rank].cuda(), handle=got.handle, weights=case.weights[rank].cuda(), zero_padding=True)
+                        torch.cuda.synchronize()
+                        assert_dispatch_matches(again, case.xs, case.indices, case.weights, case.num_experts, rank,
+                                                expand=expand, alignment=alignment, zero_padding=True)
+                        checks += 1
         finally:
             ext.set_fused_limits(*before)
         # back-to-back async operations reusing the window without host syncs in between
