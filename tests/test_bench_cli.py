@@ -27,3 +27,28 @@ def test_defaults_are_single_gpu_and_short():
         sys.argv = argv
     assert args.gpus == 1 and args.steps <= 50 and args.warmup >= 3
     assert (args.tokens, args.hidden, args.experts, args.topk) == (4096, 7168, 256, 8)
+
+
+def test_clock_sampler_keeps_only_samples_inside_the_timed_windows(monkeypatch):
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    class NoChild:
+        def __init__(self, *a, **k):
+            raise OSError("no child processes in this test")
+
+    monkeypatch.setattr(bench.subprocess, "Popen", NoChild)
+    sampler = bench.ClockSampler(0, "GPU-00000000")
+    assert sampler.wait_ready(0.05) is False  # no child: gives up at once, never blocks a run
+    sampler.windows = [[100.0, 101.0], [105.0, 106.0]]
+    with open(sampler._path, "w") as f:
+        f.write("source nvml\n")
+        f.write("99.5 1200 1965 -\n")                      # before the first window
+        f.write("100.5 1900 1965 sw_power_cap\n")
+        f.write("103.0 300 1965 hw_slowdown\n")            # between the windows: not under load, ignored
+        f.write("105.5 1950 1965 -\n")
+        f.write("garbage line\n")
+    got = sampler.summary()
+    assert got["samples"] == 2 and got["sm_mhz"] == 1925.0 and got["sm_max_mhz"] == 1965.0
+    assert got["reasons"] == ["sw_power_cap"] and got["source"] == "nvml" and got["window"] == "timed regions"
+    assert not Path(sampler._path).exists()
