@@ -136,6 +136,48 @@ def test_cached_replay_and_poison(launch_path):
                     assert torch.equal(first[r].x, keep_x[r]), "earlier outputs must own their storage"
 
 
+def test_special_bit_patterns_survive_dispatch_and_combine(launch_path):
+    """Dispatch moves bits (NaN payloads, infinities, negative zero, denormals and gate weights included);
+    combine propagates non-finite values like a plain fp32 sum does."""
+    world = 2
+    case = make_case(world, kind="random", seed=3, hidden=256, tokens=12)
+    patterns = torch.tensor([0x7FC1, 0xFFFF, 0x7F80, 0xFF80, 0x8000, 0x0001, 0x8001, 0x7F7F], dtype=torch.int32).to(torch.int16)
+    xs = []
+    for r, x in enumerate(case.xs):
+        bits = x.clone().view(torch.int16)
+        bits[:, r::7] = patterns[(torch.arange(bits[:, r::7].shape[1]) + r) % len(patterns)]
+        xs.append(bits.view(torch.bfloat16))
+    ws = [w.clone() for w in case.weights]
+    ws[0].view(torch.int32)[0, 0] = 0x7FC00001  # a NaN with a payload among the gate weights
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+    with EmulatedGroup(world, cfg) as group:
+        for expand in (False, True):
+            first = group.dispatch(_to_cuda(xs), topk_idx=_to_cuda(case.indices), weights=_to_cuda(ws), do_expand=expand, alignment=4,
+                                   zero_padding=True)
+            again = group.dispatch(_to_cuda(xs), handles=[f.handle for f in first], weights=_to_cuda(ws), zero_padding=True)
+            torch.cuda.synchronize()
+            group.check_status()
+            for got in (first, again):
+                for r in range(world):
+                    assert_dispatch_matches(got[r], xs, case.indices, ws, case.num_experts, r, expand=expand, alignment=4,
+                                            zero_padding=True)
+        # combine: identity experts; a token with an infinity or a NaN in a column keeps it (or turns NaN), like the reference sum
+        back = group.combine([g.x for g in again], [f.handle for f in first])
+        torch.cuda.synchronize()
+        group.check_status()
+        for r in range(world):
+            acc = torch.zeros(xs[r].shape, dtype=torch.float32)
+            for k in range(case.num_topk):  # fp32 sum over the valid choices in ascending k, one bf16 round
+                acc = torch.where((case.indices[r][:, k] >= 0)[:, None], acc + xs[r].float(), acc)
+            want = acc.to(torch.bfloat16)
+            got = back[r].x.cpu()
+            finite = torch.isfinite(want.float())
+            assert torch.equal(torch.isnan(got.float()), torch.isnan(want.float()))
+            assert torch.equal(got.float()[finite], want.float()[finite])
+            inf = torch.isinf(want.float())
+            assert torch.equal(got.float()[inf], want.float()[inf])
+
+
 def test_many_rounds_large_hidden():
     """More rows than one grid round per warp, DeepSeek-V3 row size, 260 experts on one rank."""
     torch.manual_seed(0)
