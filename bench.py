@@ -20,6 +20,7 @@ baseline), ``--impl reference`` (the reference package; not installable offline,
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -259,6 +260,10 @@ def run_ours(args, rank, world, device, control_group):
             ext.take_phase_timings()
             ext.set_phase_timing(True)
         clocks.wait_ready()
+        # No cyclic-GC pauses inside the timed regions: a fresh dispatch has a host round trip per step, so a
+        # pause on one rank is a wait in the peer barrier for all of them.  Switched back on at the end.
+        gc.collect()
+        gc.disable()
         sync_all()
         with clocks:
             wall0 = time.perf_counter()
@@ -355,6 +360,7 @@ def run_ours(args, rank, world, device, control_group):
             clocks.extended_s = time.time() - t0
             buf.check_status()
         clock_summary = clocks.summary()
+        gc.enable()
 
     line = {
         "metric": "ep_dispatch_combine_payload_GBps",
@@ -385,6 +391,7 @@ def run_ours(args, rank, world, device, control_group):
             "allow_multiple_reduction": args.multiple_reduction,
             "l2": f"inputs larger than L2: timed steps rotate over {len(x_sets)} copies of the token matrix ({len(x_sets) * x.numel() * 2 >> 20} MiB > 126 MB); a step also writes ~1 GB of outputs/window",
             "value_formula": "(sum_ranks N_dedup_rows + combine_rows) * hidden * 2 B / max_rank device time",
+            "host": "Python cyclic GC off inside the timed regions",
         },
         "dispatch_us": disp_us,
         "combine_us": comb_us,
