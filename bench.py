@@ -96,12 +96,13 @@ class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU while the timed regions run.
 
     The sampling loop lives in a child process (NVML queries, read-only; ``nvidia-smi`` as fallback) so that
-    it never competes with the benchmark's own thread for the interpreter; the parent only notes the
+    it never competes with the benchmark's own thread for the interpreter, and it samples every 50 ms only:
+    management-library queries and kernel launches on one GPU share driver locks; the parent only notes the
     wall-clock windows of its timed regions and keeps the samples that fall inside them.  Nothing is ever
     set or reset on the GPU.
     """
 
-    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.005):
+    def __init__(self, gpu_index: int, gpu_uuid: str | None = None, period_s: float = 0.05):
         self.windows: list[list[float]] = []
         self.source = None
         self.extended_s = 0.0
@@ -175,6 +176,29 @@ class ClockSampler:
             "window": "timed regions" + (f" + {self.extended_s:.2f} s of the same steps repeated untimed right after them"
                                          if self.extended_s else ""),
         }
+
+
+def merge_clock_summaries(per_rank: list[dict]) -> dict:
+    """One record for the job from every rank's own GPU: the slowest median clock, the union of the reasons."""
+    medians = [s["sm_mhz"] for s in per_rank if s["sm_mhz"] is not None]
+    tops = [s["sm_max_mhz"] for s in per_rank if s["sm_max_mhz"] is not None]
+    return {
+        "sm_mhz": min(medians) if medians else None,
+        "sm_max_mhz": max(tops) if tops else None,
+        "reasons": sorted({r for s in per_rank for r in s["reasons"]}),
+        "samples": sum(s["samples"] for s in per_rank),
+        "source": per_rank[0]["source"],
+        "window": per_rank[0]["window"],
+        "per_rank_sm_mhz": [s["sm_mhz"] for s in per_rank],
+    }
+
+
+def gather_clock_summaries(summary: dict, world: int, control_group) -> dict:
+    import torch.distributed as dist
+
+    gathered = [None] * world
+    dist.all_gather_object(gathered, summary, group=control_group)
+    return merge_clock_summaries(gathered)
 
 
 def make_inputs(args, rank, world, device):
@@ -347,10 +371,10 @@ def run_ours(args, rank, world, device, control_group):
                 "d2h_bytes_per_step": 4,
             }
         timed_wall_s = (ms_per_step + (e2e["ms_per_step"] if e2e else 0.0)) * 1e-3 * args.steps  # same value on every rank
-        if timed_wall_s < 0.25:
+        if timed_wall_s < 0.5:
             # The timed regions are shorter than a few sampling periods: repeat the same device-timed
             # steps (not counted in any number) so that the clock record shows the GPU under this load.
-            extra = max(args.steps, int(0.3 / max(ms_per_step * 1e-3, 1e-6)))
+            extra = max(args.steps, int(0.5 / max(ms_per_step * 1e-3, 1e-6)))
             sync_all()
             t0 = time.time()
             with clocks:
@@ -359,7 +383,7 @@ def run_ours(args, rank, world, device, control_group):
                 sync_all()
             clocks.extended_s = time.time() - t0
             buf.check_status()
-        clock_summary = clocks.summary()
+        clock_summary = gather_clock_summaries(clocks.summary(), world, control_group)
         gc.enable()
 
     line = {
@@ -494,7 +518,7 @@ def run_nccl(args, rank, world, device, control_group):
         "dispatch_us": float(d.item()) * 1e3,
         "combine_us": (ms_per_step - float(d.item())) * 1e3,
         "gpu_launches": 0,
-        "clocks": clocks.summary(),
+        "clocks": gather_clock_summaries(clocks.summary(), world, control_group),
     }
 
 

@@ -52,3 +52,16 @@ def test_clock_sampler_keeps_only_samples_inside_the_timed_windows(monkeypatch):
     assert got["samples"] == 2 and got["sm_mhz"] == 1925.0 and got["sm_max_mhz"] == 1965.0
     assert got["reasons"] == ["sw_power_cap"] and got["source"] == "nvml" and got["window"] == "timed regions"
     assert not Path(sampler._path).exists()
+
+
+def test_clock_records_of_all_ranks_are_merged_pessimistically():
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    a = {"sm_mhz": 1950.0, "sm_max_mhz": 1965.0, "reasons": [], "samples": 5, "source": "nvml", "window": "timed regions"}
+    b = {"sm_mhz": 1400.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 4, "source": "nvml", "window": "timed regions"}
+    c = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": None, "window": "timed regions"}
+    got = bench.merge_clock_summaries([a, b, c])
+    assert got["sm_mhz"] == 1400.0 and got["sm_max_mhz"] == 1965.0 and got["reasons"] == ["sw_power_cap"] and got["samples"] == 9
+    assert got["per_rank_sm_mhz"] == [1950.0, 1400.0, None]
+    assert bench.merge_clock_summaries([c])["sm_mhz"] is None
