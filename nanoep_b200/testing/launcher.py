@@ -17,6 +17,11 @@ from pathlib import Path
 
 
 def run_logged(command, *, log: Path, cwd, env=None, timeout: float = 300) -> int:
+    # NANOEP_LOG_DIR keeps the workers' logs in one place after the test's temporary directory is gone
+    # (the reference has NANO_EP_LOG_DIR for the same purpose, docs/testing.md:26).
+    keep = os.environ.get("NANOEP_LOG_DIR")
+    if keep:
+        log = Path(keep) / log.name
     log.parent.mkdir(parents=True, exist_ok=True)
     with log.open("w") as output:
         process = subprocess.Popen(command, cwd=cwd, env=env, stdout=output, stderr=subprocess.STDOUT, start_new_session=True)
@@ -47,4 +52,5 @@ def run_ranks(target: str, nproc: int, *, args=(), log: Path, cwd, timeout: floa
     ]
     command += (["-m", target] if as_module else [target]) + list(args)
     code = run_logged(command, log=log, cwd=cwd, env=full_env, timeout=timeout)
-    return code, log.read_text()
+    keep = os.environ.get("NANOEP_LOG_DIR")
+    return code, (Path(keep) / log.name if keep else log).read_text()
