@@ -64,6 +64,27 @@ def all_kinds(rank, world, multiple):
     return True
 
 
+def special_bits(rank, world):
+    """Dispatch moves bits: NaN payloads, infinities, negative zero and denormals arrive unchanged."""
+    case = make_case(world, kind="random", seed=3, hidden=64, tokens=9)
+    patterns = torch.tensor([0x7FC1, 0xFFFF, 0x7F80, 0xFF80, 0x8000, 0x0001, 0x8001, 0x7F7F], dtype=torch.int32).to(torch.int16)
+    xs = []
+    for r, x in enumerate(case.xs):
+        bits = x.clone().view(torch.int16)
+        bits[:, r::5] = patterns[(torch.arange(bits[:, r::5].shape[1]) + r) % len(patterns)]
+        xs.append(bits.view(torch.bfloat16))
+    ws = [w.clone() for w in case.weights]
+    ws[0].view(torch.int32)[0, 0] = 0x7FC00001
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+    with CpuBuffer(dist.group.WORLD, cfg) as buf:
+        for expand in (False, True):
+            got = buf.dispatch(xs[rank], topk_idx=case.indices[rank], weights=ws[rank], do_expand=expand, alignment=4, zero_padding=True)
+            assert_dispatch_matches(got, xs, case.indices, ws, case.num_experts, rank, expand=expand, alignment=4, zero_padding=True)
+            again = buf.dispatch(xs[rank], handle=got.handle, weights=ws[rank], zero_padding=True)
+            assert_dispatch_matches(again, xs, case.indices, ws, case.num_experts, rank, expand=expand, alignment=4, zero_padding=True)
+    return True
+
+
 def _choice_values(case, world):
     gen = torch.Generator().manual_seed(11)
     return [torch.randn(idx.shape[0], case.num_topk, case.hidden, generator=gen).to(torch.bfloat16) for idx in case.indices]

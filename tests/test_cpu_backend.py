@@ -16,6 +16,10 @@ def test_all_kinds_against_oracle(world, multiple):
     assert all(run_gloo(world, cpu_workers.all_kinds, multiple, timeout=300))
 
 
+def test_special_bit_patterns_are_moved_unchanged():
+    assert all(run_gloo(2, cpu_workers.special_bits))
+
+
 def test_argument_contract_and_lifetime():
     assert all(run_gloo(2, cpu_workers.misuse))
 
