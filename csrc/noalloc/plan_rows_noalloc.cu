@@ -3,12 +3,13 @@
 
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <mutex>
 
 namespace {
 
-// Cursor storage shared by every call on a device: [0] row cursor, [64 + l] slot cursor of local
-// expert l.  File-scope device memory: part of the library image, never allocated at run time.
+// Cursor storage shared by every call on a device: [0] row cursor, [1] count of slots that fell outside
+// their expert's range, [64 + l] slot cursor of local expert l.  File-scope device memory: part of the library image, never allocated at run time.
 static __device__ __align__(256) int g_plan_scratch[NEP_NOALLOC_MAX_LOCAL_EXPERTS + 64];
 
 constexpr int kThreads = 256;
@@ -84,12 +85,22 @@ __global__ void __launch_bounds__(kThreads) plan_rows_kernel(const int* __restri
             int v = -1;
             if (e >= lo && e < lo + Le) {
                 const int le = e - lo;
-                v = expand ? eoff[le] + atomicAdd(&expert_cursor[le], 1) : le;
+                v = le;
+                if (expand) {
+                    v = eoff[le] + atomicAdd(&expert_cursor[le], 1);
+                    if (v < 0 || v >= eoff[le + 1]) {  // offsets that do not fit the routing: never hand out a foreign slot
+                        atomicAdd(scratch + 1, 1);
+                        v = -1;
+                    }
+                }
             }
             m[2 + k] = v;
         }
     }
 }
+
+// Row count of the call, or -1 when a slot fell outside its expert's range.
+__global__ void publish_count_kernel(const int* scratch, int* row_count_out) { *row_count_out = scratch[1] != 0 ? -1 : scratch[0]; }
 
 }  // namespace
 
@@ -97,10 +108,12 @@ extern "C" const char* nep_noalloc_last_error(void) { return t_last_error; }
 
 extern "C" int nep_plan_rows_noalloc(const int* topk_i32, int tokens, int topk, int source_rank, int expert_lo, int local_experts,
                                      const int* expert_offsets, int expand, int* meta_out, int* row_count_out, void* stream) {
-    if (topk_i32 == nullptr || meta_out == nullptr || row_count_out == nullptr || tokens < 0 || topk <= 0 || local_experts <= 0 ||
+    t_last_error = "";
+    if ((topk_i32 == nullptr && tokens > 0) || (meta_out == nullptr && tokens > 0) || row_count_out == nullptr || tokens < 0 || topk <= 0 || local_experts <= 0 ||
         expert_lo < 0 || source_rank < 0 || (expand && expert_offsets == nullptr))
         return NEP_NOALLOC_BAD_ARGUMENT;
     if (local_experts > NEP_NOALLOC_MAX_LOCAL_EXPERTS || topk > 32 || tokens > (1 << 24)) return NEP_NOALLOC_TOO_LARGE;
+    if (expert_lo > INT_MAX - local_experts) return NEP_NOALLOC_BAD_ARGUMENT;  // expert_lo + local_experts must fit an int
     int* scratch = nullptr;
     const int setup = scratch_for_current_device(&scratch);
     if (setup != NEP_NOALLOC_OK) return setup;
@@ -111,11 +124,16 @@ extern "C" int nep_plan_rows_noalloc(const int* topk_i32, int tokens, int topk, 
         const int chunks = (tokens + 31) / 32;
         int blocks = (chunks + (kThreads / 32) - 1) / (kThreads / 32);
         if (blocks > 1184) blocks = 1184;  // 148 SMs x 8 resident blocks
-        plan_rows_kernel<<<blocks, kThreads, 0, s>>>(topk_i32, tokens, topk, source_rank, expert_lo, local_experts, expert_offsets, expand,
-                                                      meta_out, scratch);
-        e = cudaGetLastError();
+        // cudaLaunchKernel returns this launch's own error; an older sticky error is not picked up and blamed on it
+        void* args[] = {(void*)&topk_i32, (void*)&tokens, (void*)&topk, (void*)&source_rank, (void*)&expert_lo, (void*)&local_experts,
+                        (void*)&expert_offsets, (void*)&expand, (void*)&meta_out, (void*)&scratch};
+        e = cudaLaunchKernel((const void*)plan_rows_kernel, dim3(blocks), dim3(kThreads), args, 0, s);
     }
-    if (e == cudaSuccess) e = cudaMemcpyAsync(row_count_out, scratch, sizeof(int), cudaMemcpyDeviceToDevice, s);
+    if (e == cudaSuccess) {
+        const int* scratch_in = scratch;
+        void* args[] = {(void*)&scratch_in, (void*)&row_count_out};
+        e = cudaLaunchKernel((const void*)publish_count_kernel, dim3(1), dim3(1), args, 0, s);
+    }
     if (e != cudaSuccess) {
         t_last_error = cudaGetErrorString(e);
         return NEP_NOALLOC_CUDA_ERROR;

@@ -22,7 +22,10 @@
  *   - The cursor array (NEP_NOALLOC_SCRATCH_BYTES = 16640 bytes) lives in every GPU that loads this
  *     library, from load to process exit.
  *   - The first call on each device looks up the device address of that array (the device must be
- *     current, as for every call).  Make that first call before any stream capture begins.
+ *     current, as for every call) and, when the CUDA runtime loads modules lazily, also loads this
+ *     library's device code, which the driver may back with memory of its own.  Make that first call
+ *     during start-up: before any stream capture begins and before a phase in which nothing may be
+ *     allocated.
  *   - Every call on a device shares the one array and starts by clearing it on `stream`.  Two calls
  *     that overlap on the GPU (different streams, no ordering) race on it; order them.
  *   - All pointers are device pointers valid on the current device; `stream` is a cudaStream_t.
@@ -47,7 +50,8 @@ enum {
 /* topk_i32        [tokens, topk] int32 global expert ids, -1 = masked
  * expert_offsets  [local_experts + 1] int32 exclusive padded offsets (read only when expand != 0)
  * meta_out        [>= kept tokens, topk + 2] int32; size it for `tokens` rows to be safe
- * row_count_out   one int32: number of rows written
+ * row_count_out   one int32: number of rows written, or -1 when expert_offsets do not fit the routing
+ *                 (a slot fell outside its expert's range; such choices are written as -1)
  * Returns one of the codes above.  Work is enqueued on `stream`; outputs are valid once it drains. */
 int nep_plan_rows_noalloc(const int* topk_i32, int tokens, int topk, int source_rank, int expert_lo, int local_experts,
                           const int* expert_offsets, int expand, int* meta_out, int* row_count_out, void* stream);

@@ -45,19 +45,6 @@ def source_dir() -> Path:
     raise FileNotFoundError("nanoep_b200 native sources not found")
 
 
-def cutlass_include_dirs() -> list[str]:
-    """Vendored CUTLASS/CuTe header trees (optional; only some kernels include them)."""
-    found = []
-    for site in sys.path:
-        for rel in ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include"):
-            p = Path(site) / rel
-            if p.is_dir():
-                found.append(str(p))
-        if found:
-            break
-    return found[:1]
-
-
 def sources_hash(extra: tuple[str, ...] = ()) -> str:
     h = hashlib.sha256()
     root = source_dir()
@@ -101,7 +88,7 @@ def build_extension(verbose: bool | None = None, force: bool = False):
     module = cpp_extension.load(
         name=EXT_NAME,
         sources=[str(root / s) for s in SOURCES],
-        extra_include_paths=[str(root)] + cutlass_include_dirs(),
+        extra_include_paths=[str(root)],
         extra_cflags=["-O2", "-std=c++17"],
         extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", *ARCH_FLAGS],
         extra_ldflags=["-lcuda", "-lstdc++", "-lm"],

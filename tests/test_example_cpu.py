@@ -25,3 +25,17 @@ def test_example_moe_cpu(tmp_path, extra):
     )
     assert code == 0, text[-3000:]
     assert text.count("NANOEP_MOE_OK=") == 2, text[-3000:]
+
+
+def test_acceptance_profiles_cpu(tmp_path):
+    """The acceptance worker itself (all profiles that are small enough for the CPU backend), 2 Gloo ranks."""
+    from tests.acceptance_worker import PROFILES
+
+    small = [n for n in PROFILES if not n.startswith("wide-")]
+    code, text = run_ranks(
+        str(ROOT / "tests" / "acceptance_worker.py"), 2, log=tmp_path / "accept.log", cwd=ROOT, timeout=600, as_module=False,
+        env={**__import__("os").environ, "NANOEP_ACCEPT_BACKEND": "cpu", "NANOEP_ACCEPT_PROFILES": ",".join(small)},
+    )
+    assert code == 0, text[-3000:]
+    for name in small:
+        assert text.count(f"NANOEP_ACCEPT_OK={name} ") == 2, (name, text[-3000:])

@@ -28,10 +28,21 @@ def test_public_api_worker(tmp_path, nproc):
         assert f"NANOEP_RANK_OK={rank} " in text, text[-4000:]
 
 
-@pytest.mark.parametrize("extra", [["--async-op", "--cached"], ["--layout", "compact", "--pattern", "uneven"], ["--pattern", "skew", "--tokens", "256", "--hidden", "7168", "--topk", "8"]])
-def test_example_moe(tmp_path, extra):
+def test_example_moe_acceptance_profiles(tmp_path):
+    """All delivery profiles of the forward MoE example (both layouts x four routing patterns, up to
+    256 tokens x 7168 x top-8, async + cached) in one launch per world size."""
+    from tests.acceptance_worker import PROFILES
+
     nproc = 2 if _gpus() < 4 else 4
-    code, text = run_ranks("nanoep_b200.examples.moe", nproc, args=extra, log=tmp_path / "moe.log", cwd=ROOT, timeout=300)
+    code, text = run_ranks(str(ROOT / "tests" / "acceptance_worker.py"), nproc, log=tmp_path / "accept.log", cwd=ROOT, timeout=600, as_module=False)
+    assert code == 0, text[-4000:]
+    for name in PROFILES:
+        assert text.count(f"NANOEP_ACCEPT_OK={name} ") == nproc, (name, text[-4000:])
+
+
+def test_example_moe_cli(tmp_path):
+    nproc = 2 if _gpus() < 4 else 4
+    code, text = run_ranks("nanoep_b200.examples.moe", nproc, args=["--async-op", "--cached"], log=tmp_path / "moe.log", cwd=ROOT, timeout=300)
     assert code == 0, text[-4000:]
     assert text.count("NANOEP_MOE_OK=") == nproc, text[-4000:]
 

@@ -23,11 +23,59 @@ def test_no_cluster_multicast_loads_and_no_traps():
         assert not banned.search(text), f"{path} uses a construct that is banned in this project"
 
 
+def _loops(text):
+    """(header, body) of every `for`/`while`/`do` loop in C-like source; bodies are brace-matched, a loop
+    without braces ends at its first semicolon."""
+    for m in re.finditer(r"\b(for|while|do)\b", text):
+        i = m.end()
+        header = ""
+        if m.group(1) != "do":
+            while i < len(text) and text[i].isspace():
+                i += 1
+            if i >= len(text) or text[i] != "(":
+                continue
+            depth, j = 0, i
+            while j < len(text):
+                depth += text[j] == "("
+                depth -= text[j] == ")"
+                j += 1
+                if depth == 0:
+                    break
+            header, i = text[i:j], j
+        while i < len(text) and text[i].isspace():
+            i += 1
+        if i < len(text) and text[i] == "{":
+            depth, j = 0, i
+            while j < len(text):
+                depth += text[j] == "{"
+                depth -= text[j] == "}"
+                j += 1
+                if depth == 0:
+                    break
+            body = text[i:j]
+        else:
+            j = text.find(";", i)
+            body = text[i : j + 1]
+            if m.group(1) == "while" and not body.strip(" ;"):
+                continue  # the tail of a do { } while (...);
+        yield header, body
+
+
 def test_every_device_wait_is_bounded():
-    text = "".join((ROOT / "csrc" / name).read_text() for name in ("prim.cuh", "tc_prim.cuh", "grouped_gemm_sm100.cu", "grouped_gemm_sm100_2cta.cu"))
-    # each spin loop compares a timer against a limit
-    for loop in re.findall(r"while \((?:!mbar_try|ld_acquire)[^{]*\{?[^}]*", text):
-        assert "timeout_ns" in loop or "limit_ns" in loop, loop
+    """Every loop in the native sources that polls memory, an mbarrier or sleeps must compare a timer (or an
+    iteration count) against a limit inside the loop."""
+    polls = re.compile(r"ld_acquire|ld_relaxed_sys|try_wait|mbar_try|__nanosleep|volatile")
+    bounded = re.compile(r"timeout_ns|limit_ns|deadline|max_spins|kMaxSpins")
+    checked = 0
+    for path in _native_sources():
+        if path.suffix == ".cpp" or path.name.endswith(".hpp"):
+            continue  # host code: its waits are wall-clock bounded and tested separately
+        text = re.sub(r"//[^\n]*", "", path.read_text())
+        for header, body in _loops(text):
+            if polls.search(header) or (polls.search(body) and re.search(r"\b(break|return)\b", body) and not re.search(r"\bfor\b|\bwhile\b", body[1:])):
+                checked += 1
+                assert bounded.search(header + body), f"{path.name}: unbounded wait loop: {header} {body[:200]}"
+    assert checked >= 6, "the scan found no wait loops; the patterns are stale"
 
 
 def test_build_lists_existing_sources():

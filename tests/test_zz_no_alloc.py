@@ -92,3 +92,26 @@ def test_sizes_beyond_the_maximum_are_rejected():
     wide = torch.zeros(4, 33, dtype=torch.int32, device="cuda")
     assert noalloc.plan_rows_noalloc(wide, 0, 0, 8, None, False, meta_out, count) == noalloc.TOO_LARGE
     assert noalloc.plan_rows_noalloc(topk32, 0, 0, 8, None, True, meta_out, count) == noalloc.BAD_ARGUMENT
+
+
+def test_empty_input_and_inconsistent_offsets():
+    K, L = 2, 4
+    meta_out = torch.full((8, K + 2), -7, dtype=torch.int32, device="cuda")
+    count = torch.full((1,), 99, dtype=torch.int32, device="cuda")
+    empty = torch.zeros(0, K, dtype=torch.int32, device="cuda")
+    assert noalloc.plan_rows_noalloc(empty, 0, 0, L, None, False, meta_out, count) == noalloc.OK
+    torch.cuda.synchronize()
+    assert int(count.item()) == 0 and (meta_out == -7).all()
+    # four tokens all choose expert 1, but the offsets leave it two slots: the count reports the misfit
+    # and no slot outside expert 1's range is handed out
+    topk32 = torch.tensor([[1, -1]] * 4, dtype=torch.int32, device="cuda")
+    offsets = torch.tensor([0, 2, 4, 6, 8], dtype=torch.int32, device="cuda")
+    assert noalloc.plan_rows_noalloc(topk32, 0, 0, L, offsets, True, meta_out, count) == noalloc.OK
+    torch.cuda.synchronize()
+    assert int(count.item()) == -1
+    slots = meta_out[:4, 2].cpu()
+    assert sorted(s for s in slots.tolist() if s >= 0) == [2, 3] and (slots == -1).sum() == 2
+    # the next call starts from cleared cursors
+    assert noalloc.plan_rows_noalloc(topk32[:2].contiguous(), 0, 0, L, offsets, True, meta_out, count) == noalloc.OK
+    torch.cuda.synchronize()
+    assert int(count.item()) == 2
