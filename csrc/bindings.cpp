@@ -167,6 +167,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });
     m.def("format_status", &nep::format_status);
+    m.def("peer_access_error", &nep::peer_access_error, py::arg("own_rank"), py::arg("peer_rank"), py::arg("own_device"),
+          py::arg("peer_device"), py::arg("can_access"), py::arg("access_supported"));
     m.def("status_name", [](uint32_t code) { return std::string(nep::status_name(code)); });
     m.def("kernel_table", [] {
         nep::KernelInfo info[32];

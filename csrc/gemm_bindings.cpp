@@ -106,8 +106,10 @@ void bind_gemm(pybind11::module_& m) {
             g.args.ldo = int(n_out);
             if (tile_ready.has_value()) {
                 TORCH_CHECK(tile_expected.has_value() && tile_ready->scalar_type() == at::kInt && tile_expected->scalar_type() == at::kInt &&
-                                tile_ready->numel() >= g.args.m_blocks && tile_expected->numel() >= g.args.m_blocks,
-                            "tile_ready/tile_expected must be int32 tensors with one entry per 128-row block");
+                                tile_ready->numel() >= g.args.m_blocks && tile_expected->numel() >= g.args.m_blocks &&
+                                tile_ready->is_cuda() && tile_expected->is_cuda() && tile_ready->device() == a.device() &&
+                                tile_expected->device() == a.device() && tile_ready->is_contiguous() && tile_expected->is_contiguous(),
+                            "tile_ready/tile_expected must be contiguous int32 tensors on the activations' device with one entry per 128-row block");
                 g.args.tile_ready = tile_ready->data_ptr<int>();
                 g.args.tile_expected = tile_expected->data_ptr<int>();
             }
@@ -149,9 +151,10 @@ void bind_gemm(pybind11::module_& m) {
             auto g = prepare(a, w, expert_offsets, status, gemm::kScatter, timeout_s);
             const WindowLayout& L = window.layout();
             TORCH_CHECK(w.size(1) == L.hidden, "down-projection N must equal the buffer's hidden size");
-            TORCH_CHECK(slot_map.is_cuda() && slot_map.scalar_type() == at::kInt && slot_map.numel() == a.size(0), "slot_map must be int32 [rows]");
+            TORCH_CHECK(slot_map.is_cuda() && slot_map.scalar_type() == at::kInt && slot_map.numel() == a.size(0) && slot_map.is_contiguous(),
+                        "slot_map must be contiguous int32 [rows]");
             TORCH_CHECK(recv_metadata.is_cuda() && recv_metadata.scalar_type() == at::kInt && recv_metadata.dim() == 2 &&
-                            recv_metadata.size(1) == L.topk + 2,
+                            recv_metadata.size(1) == L.topk + 2 && recv_metadata.is_contiguous(),
                         "recv_metadata must be int32 [N, topk + 2]");
             g.args.slot_map = slot_map.data_ptr<int>();
             g.args.recv_metadata = recv_metadata.data_ptr<int>();
@@ -165,6 +168,8 @@ void bind_gemm(pybind11::module_& m) {
             g.args.ret_offset = L.ret_offset + parity * L.ret_stride;
             g.args.max_tokens = L.max_tokens;
             g.args.topk = L.topk;
+            g.args.ranks = L.ranks;
+            g.args.recv_rows = int(recv_metadata.size(0));
             g.args.ldo = L.hidden;
             if (a.size(0) == 0) return;
             const int grid = max_ctas > 0 ? std::min<int>(g.grid, int(max_ctas)) : g.grid;

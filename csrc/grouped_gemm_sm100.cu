@@ -112,7 +112,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = threadIdx.x; i <= args.num_experts; i += kThreads) sh.offsets[i] = int(args.expert_offsets[i]);
+    for (int i = threadIdx.x; i <= args.num_experts; i += kThreads) {
+        const int64_t off = args.expert_offsets[i];
+        sh.offsets[i] = int(off);
+        // one expert per 128-row block: offsets must be multiples of 128, start at 0 and end at the row count
+        if ((off & 127) != 0 || (i == 0 && off != 0) || (i == args.num_experts && off != int64_t(args.m_blocks) * BM)) {
+            sh.abort = 1;
+            if (atomicCAS(args.status, 0u, uint32_t(kGemmBadOffsets)) == 0u) args.status[1] = uint32_t(i);
+        }
+    }
     if (warp == 1) tmem_alloc(&sh.tmem_base, kTmemCols);
     tc_fence_before();
     __syncthreads();
@@ -286,6 +294,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
                     const int* meta = args.recv_metadata + int64_t(recv_row) * (args.topk + 2);
                     const int src = meta[0], tok = meta[1];
                     scale = args.slot_weights != nullptr ? args.slot_weights[row] : 1.f;
+                    if (recv_row >= args.recv_rows || src < 0 || src >= args.ranks || tok < 0 || tok >= args.max_tokens) {
+                        // impossible provenance: skip the row and report it, as the push kernel does
+                        if (atomicCAS(args.status, 0u, uint32_t(kGemmBadMetadata)) == 0u) args.status[1] = uint32_t(row);
+                    } else
                     out_row = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(args.peers[src]) + args.ret_offset +
                                                                (int64_t(k) * args.max_tokens + tok) * int64_t(args.ldo) * 2) +
                               nt * BN;

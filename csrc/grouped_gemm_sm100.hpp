@@ -9,7 +9,7 @@ namespace nep {
 namespace gemm {
 
 enum Mode : int { kPlain = 0, kSwiGLU = 1, kScatter = 2 };
-enum GemmStatus : uint32_t { kGemmOk = 0, kGemmPipeTimeout = 101, kGemmTileTimeout = 102 };
+enum GemmStatus : uint32_t { kGemmOk = 0, kGemmPipeTimeout = 101, kGemmTileTimeout = 102, kGemmBadOffsets = 103, kGemmBadMetadata = 104 };
 
 struct Args {
     const int64_t* expert_offsets;  // [E+1] padded exclusive row offsets, multiples of 128
@@ -35,6 +35,8 @@ struct Args {
     int64_t ret_offset;         // byte offset of the return partitions (parity applied) in a window
     int64_t max_tokens;
     int topk;
+    int ranks;      // kScatter: valid source ranks are [0, ranks)
+    int recv_rows;  // kScatter: rows of recv_metadata
 };
 
 size_t shared_bytes(int mode, int stages);

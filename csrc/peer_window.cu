@@ -50,8 +50,10 @@ PeerWindow::PeerWindow(int rank, int world, const WindowLayout& layout, double w
         mailbox_dev_ = static_cast<volatile int64_t*>(dev);
         status_host_dev_ = reinterpret_cast<volatile uint32_t*>(static_cast<char*>(dev) + 64);
     }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
+        if (order_event_) cudaEventDestroy(order_event_);
         if (pinned_) cudaFreeHost(pinned_);
         cudaFree(base_);
         base_ = nullptr;
@@ -68,6 +70,20 @@ PeerWindow::~PeerWindow() {
     } else if (!closed_ && base_ != nullptr) {
         std::fprintf(stderr, "nanoep_b200: PeerWindow destroyed without close(); leaking the window\n");
     }
+}
+
+std::string peer_access_error(int own_rank, int peer_rank, int own_device, int peer_device, bool can_access, bool access_supported) {
+    char buf[256];
+    if (peer_device == own_device) {
+        std::snprintf(buf, sizeof(buf), "rank %d and rank %d share CUDA device %d; every rank needs its own GPU", own_rank, peer_rank, own_device);
+        return buf;
+    }
+    if (!can_access || !access_supported) {
+        std::snprintf(buf, sizeof(buf), "CUDA device %d (rank %d) has no peer access to device %d (rank %d); NVLink or PCIe P2P is required",
+                      own_device, own_rank, peer_device, peer_rank);
+        return buf;
+    }
+    return std::string();
 }
 
 std::string PeerWindow::export_handle() {
@@ -90,8 +106,17 @@ void PeerWindow::import_handles(const std::vector<std::string>& handles) {
             check(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
             peers_[p] = mapped;
             imported_[p] = true;
-            // Opening with lazy peer access already fails when the two GPUs cannot reach each other;
-            // that the ranks sit on distinct GPUs is checked by UUID before any handle is exchanged.
+            // The mapping alone proves little: check where the memory lives and that this GPU may load from,
+            // store to and bulk-copy into it (same role as the reference's checks, csrc/peer.cu:95-126).
+            cudaPointerAttributes where{};
+            check(cudaPointerGetAttributes(&where, mapped), "cudaPointerGetAttributes(peer window)");
+            int can = 0, supported = 0;
+            if (where.device != device_) {
+                check(cudaDeviceCanAccessPeer(&can, device_, where.device), "cudaDeviceCanAccessPeer");
+                check(cudaDeviceGetP2PAttribute(&supported, cudaDevP2PAttrAccessSupported, device_, where.device), "cudaDeviceGetP2PAttribute");
+            }
+            const std::string problem = peer_access_error(rank_, p, device_, where.device, can != 0, supported != 0);
+            if (!problem.empty()) throw std::runtime_error(problem);
         }
     } catch (...) {
         for (int p = 0; p < world_; ++p)
@@ -136,6 +161,8 @@ void PeerWindow::close() {
     if (connected_ && !unmapped_) throw std::runtime_error("close_peer_mappings() must run on every rank before close()");
     cudaError_t e = cudaFree(base_);
     if (pinned_) cudaFreeHost(pinned_);
+    if (order_event_) cudaEventDestroy(order_event_);
+    order_event_ = nullptr;
     base_ = nullptr;
     pinned_ = nullptr;
     closed_ = true;
@@ -223,7 +250,17 @@ void PeerWindow::clear_status(cudaStream_t stream) {
     failed_ = false;
 }
 
+void PeerWindow::order_after_last(cudaStream_t stream) {
+    if (has_last_ && last_stream_ != stream) {
+        check(cudaEventRecord(order_event_, last_stream_), "record previous operation's stream");
+        check(cudaStreamWaitEvent(stream, order_event_, 0), "order behind previous operation");
+    }
+    last_stream_ = stream;
+    has_last_ = true;
+}
+
 void PeerWindow::barrier(cudaStream_t stream) {
+    order_after_last(stream);
     BarrierParams p{};
     p.c = common();
     p.epoch = reserve_epochs(1);

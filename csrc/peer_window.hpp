@@ -67,6 +67,12 @@ public:
     // Standalone barrier on `stream` (shares the epoch sequence with the fused barriers).
     void barrier(cudaStream_t stream);
 
+    // Operations of one window must reach the GPU in the order in which they reserved their epochs, whatever
+    // stream each runs on: signals only grow, and a region's parity copy is reused two operations later.
+    // Called at the start of every operation with the stream it will run on: when the previous operation ran
+    // on another stream, `stream` is made to wait for everything enqueued on that stream so far.
+    void order_after_last(cudaStream_t stream);
+
     // Launch counter for diagnostics and benchmarks.
     static int64_t launches;
 
@@ -84,8 +90,13 @@ private:
     volatile uint32_t* status_host_ = nullptr;  // host pointer
     volatile uint32_t* status_host_dev_ = nullptr;
     void* pinned_ = nullptr;
+    cudaStream_t last_stream_ = nullptr;
+    bool has_last_ = false;
+    cudaEvent_t order_event_ = nullptr;
 };
 
+// Empty when `own_device` may use `peer_device`'s window, else the reason (distinct GPUs and peer access are required).
+std::string peer_access_error(int own_rank, int peer_rank, int own_device, int peer_device, bool can_access, bool access_supported);
 const char* status_name(uint32_t code);
 std::string format_status(uint32_t code, uint32_t detail, uint32_t tag, int rank);
 

@@ -162,9 +162,10 @@ cudaEvent_t handover_event(int slot) {
     return events[slot];
 }
 
-Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bool async_op) {
+Streams order_inputs(const std::vector<PeerWindow*>& wins, int64_t comm_handle, int64_t previous_event, int device, bool async_op) {
     auto compute = c10::cuda::getCurrentCUDAStream(device);
     auto comm = c10::cuda::getStreamFromExternal(reinterpret_cast<cudaStream_t>(comm_handle), device);
+    const c10::cuda::CUDAStream work = async_op ? comm : compute;
     if (async_op) {
         if (previous_event != -1) {
             cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
@@ -173,21 +174,12 @@ Streams order_inputs(int64_t comm_handle, int64_t previous_event, int device, bo
             cuda_check(cudaEventRecord(ready, compute.stream()), "record caller stream");
             cuda_check(cudaStreamWaitEvent(comm.stream(), ready, 0), "wait caller stream");
         }
-        return Streams{compute, comm, comm};
-    }
-    if (previous_event != -1)
+    } else if (previous_event != -1) {
         cuda_check(cudaStreamWaitEvent(compute.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
-    // An idle communication stream (the usual case for synchronous callers) needs no hand-over.
-    const cudaError_t busy = cudaStreamQuery(comm.stream());
-    if (busy == cudaErrorNotReady) {
-        (void)cudaGetLastError();  // "not ready" is an answer, not an error to keep
-        cudaEvent_t tail = handover_event(1);
-        cuda_check(cudaEventRecord(tail, comm.stream()), "record comm stream");
-        cuda_check(cudaStreamWaitEvent(compute.stream(), tail, 0), "wait comm stream");
-    } else {
-        cuda_check(busy, "query comm stream");
     }
-    return Streams{compute, comm, compute};
+    // Behind the window's previous operation, whichever stream that ran on (free when it is the same stream).
+    for (PeerWindow* w : wins) w->order_after_last(work.stream());
+    return Streams{compute, comm, work};
 }
 
 // Every operation carries its barrier epoch and buffer parity as kernel arguments, so a captured
@@ -261,7 +253,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
     reject_graph_capture(device, fresh ? "fresh dispatch waits for receive counts on the host" : "barrier epochs and buffer parities are kernel arguments");
 
-    const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
+    const Streams s = order_inputs(wins, comm_stream, previous_event, device, async_op);
     // Outputs live in the consumer stream's pool: the caller's stream when the call completes on it,
     // the comm stream when completion is handed over through an event.
     const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
@@ -494,7 +486,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
     reject_graph_capture(device, "barrier epochs and buffer parities are kernel arguments");
 
-    const Streams s = order_inputs(comm_stream, previous_event, device, async_op);
+    const Streams s = order_inputs(wins, comm_stream, previous_event, device, async_op);
     const c10::cuda::CUDAStream consumer = async_op ? s.comm : s.compute;
     const cudaStream_t cs = s.work.stream();
     const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device);
@@ -633,6 +625,7 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
     const int device = wins[0]->device();
     c10::cuda::CUDAGuard device_guard(device);
     const cudaStream_t cs = c10::cuda::getCurrentCUDAStream(device).stream();
+    for (PeerWindow* w : wins) w->order_after_last(cs);
     const DeviceLimits lim = device_limits();
     std::vector<BarrierParams> barrier(n);
     std::vector<ReduceParams> reduce(n);
@@ -705,6 +698,7 @@ void group_barrier(const std::vector<PeerWindow*>& wins, int64_t stream) {
     }
     std::vector<BarrierParams> b(n);
     for (int i = 0; i < n; ++i) {
+        wins[i]->order_after_last(cs);
         b[i].c = wins[i]->common();
         b[i].epoch = wins[i]->reserve_epochs(1);
     }

@@ -301,3 +301,16 @@ def test_determinism_guard(monkeypatch):
     monkeypatch.setattr(cuda_buffer.deterministic, "fill_uninitialized_memory", True)
     with pytest.raises(RuntimeError, match="deterministic"):
         buf.dispatch(torch.zeros(1, 256, dtype=torch.bfloat16), topk_idx=torch.zeros(1, 2, dtype=torch.int64))
+
+
+def test_peer_access_rules():
+    """The rule the window import applies to every mapped peer: a distinct GPU that this GPU can reach."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    assert ext.peer_access_error(0, 1, 0, 1, True, True) == ""
+    same = ext.peer_access_error(2, 3, 5, 5, True, True)
+    assert "rank 2" in same and "rank 3" in same and "share CUDA device 5" in same
+    for can, supported in ((False, True), (True, False), (False, False)):
+        unreachable = ext.peer_access_error(0, 1, 0, 4, can, supported)
+        assert "no peer access" in unreachable and "device 4" in unreachable
