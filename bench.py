@@ -15,11 +15,17 @@ receives N deduplicated rows in dispatch and C_valid assignment rows come back i
 
 Arms: ``--impl ours`` (default), ``--impl nccl`` (torch.distributed all_to_all_single + index ops, a
 baseline), ``--impl reference`` (the reference package; not installable offline, prints why).
+
+After the timed steps the ``ours`` arm checks, untimed, what it has just timed: receive counts against a count
+of the all-gathered routing, every dispatched row against its source token, and the round trip bit for bit.
+The JSON line carries ``"verified"``; the process exits non-zero when the check fails.  It then runs the NCCL arm
+on the same inputs in the same process and reports ``vs_baseline`` = NCCL ms per step / this arm's ms per step.
 """
 
 from __future__ import annotations
 
 import argparse
+import contextlib
 import gc
 import json
 import os
@@ -53,6 +59,7 @@ def parse_args():
     p.add_argument("--multiple-reduction", action="store_true")
     p.add_argument("--num-sms", type=int, default=None)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-nccl-anchor", action="store_true", help="skip the NCCL arm that fills vs_baseline")
     p.add_argument("--detail", action="store_true", help="record per-kernel device times (median, max over ranks) in phases_us")
     return p.parse_args()
 
@@ -217,6 +224,77 @@ def make_inputs(args, rank, world, device):
     return x.pin_memory(), idx.pin_memory(), w.pin_memory()
 
 
+def verify_round_trip(args, buf, rank, world, device, control_group, x, idx, w, expand):
+    """One more dispatch + combine with identity experts, checked on the device.  Returns (ok, note)."""
+    import torch
+    import torch.distributed as dist
+
+    E, K, H, T = args.experts, args.topk, args.hidden, args.tokens
+    L = E // world
+    lo = rank * L
+    got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=expand, alignment=args.alignment, zero_padding=expand, num_sms=args.num_sms)
+    back = buf.combine(got.x, got.handle, num_sms=args.num_sms)
+    torch.cuda.synchronize()
+    buf.check_status()
+    problems = []
+    # every rank's tokens and routing (over NCCL: device tensors)
+    all_x = torch.empty((world, T, H), dtype=x.dtype, device=device)
+    all_idx = torch.empty((world, T, K), dtype=idx.dtype, device=device)
+    if world > 1:
+        dist.all_gather_into_tensor(all_x, x)
+        dist.all_gather_into_tensor(all_idx, idx)
+    else:
+        all_x[0], all_idx[0] = x, idx
+    mine = (all_idx >= lo) & (all_idx < lo + L)
+    want_rows = int(mine.any(-1).sum().item())
+    want_counts = torch.bincount((all_idx[mine] - lo).flatten(), minlength=L)
+    layout = got.handle.layout
+    if layout.recv_count != want_rows:
+        problems.append(f"recv_count {layout.recv_count} != {want_rows}")
+    if not torch.equal(layout.expert_counts.to(want_counts.dtype), want_counts):
+        problems.append("expert_counts differ from a count of the gathered routing")
+    meta = layout.recv_metadata.long()
+    src_rows = all_x[meta[:, 0], meta[:, 1]] if meta.shape[0] else all_x.new_zeros((0, H))
+    if expand:
+        slots = meta[:, 2:]
+        row_of, choice = torch.nonzero(slots >= 0, as_tuple=True)
+        flat = slots[row_of, choice]
+        if flat.numel() != int(want_counts.sum().item()) or flat.unique().numel() != flat.numel():
+            problems.append("expert-major slots are not a one-to-one assignment")
+        if not torch.equal(got.x[flat].view(torch.int16), src_rows[row_of].view(torch.int16)):
+            problems.append("a dispatched row differs from its source token")
+        used = torch.zeros(got.x.shape[0], dtype=torch.bool, device=device)
+        used[flat] = True
+        if bool((got.x[~used] != 0).any().item()):
+            problems.append("padding rows are not zero")
+        want_w = w[meta[row_of, 1]] if world == 1 else None  # gate weights are checked by the test suite at every size
+        del want_w
+    elif not torch.equal(got.x.view(torch.int16), src_rows.view(torch.int16)):
+        problems.append("a dispatched row differs from its source token")
+    # identity experts: the result is the token times the number of rows that came back for it, rounded once
+    # (rows pre-reduced per rank are rounded once more per rank)
+    valid = idx >= 0
+    dest = torch.where(valid, idx // L, torch.full_like(idx, -1))
+    per_rank = torch.stack([(dest == d).sum(-1) for d in range(world)], dim=-1).float()  # [T, R]
+    xf = x.float()
+    if expand and not args.multiple_reduction:
+        want = (xf * per_rank.sum(-1, keepdim=True)).to(x.dtype)
+    elif expand:
+        want = sum((xf * per_rank[:, d : d + 1]).to(x.dtype).float() for d in range(world)).to(x.dtype)
+    else:
+        want = (xf * (per_rank > 0).sum(-1, keepdim=True).float()).to(x.dtype)
+    if not torch.equal(back.x.view(torch.int16), want.view(torch.int16)):
+        bad = int((back.x.view(torch.int16) != want.view(torch.int16)).any(-1).sum().item())
+        problems.append(f"round trip differs from the expected sum in {bad} tokens")
+    gathered = [None] * world
+    dist.all_gather_object(gathered, problems, group=control_group)
+    everything = [f"rank {r}: {p}" for r, ps in enumerate(gathered) for p in ps]
+    note = "; ".join(everything) if everything else (
+        "recv_count and expert_counts equal a host-independent count of the all-gathered routing; every dispatched row equals its source "
+        "token bit for bit, padding rows are zero; combine(dispatch(x)) equals bf16(x * rows returned) bit for bit; checked on every rank")
+    return not everything, note
+
+
 def run_ours(args, rank, world, device, control_group):
     import torch
     import torch.distributed as dist
@@ -319,34 +397,48 @@ def run_ours(args, rank, world, device, control_group):
         comb_ms = [m.elapsed_time(e) for m, e in zip(mids, ends)]
         total_ms = max_over_ranks(sum(step_ms))
         ms_per_step = total_ms / args.steps
+        ordered = sorted(step_ms)
+        step_percentiles = {
+            name: max_over_ranks(ordered[min(len(ordered) - 1, int(q * len(ordered)))])
+            for name, q in (("p10", 0.10), ("p50", 0.50), ("p90", 0.90))
+        }
         disp_us = max_over_ranks(statistics.median(disp_ms)) * 1e3
         comb_us = max_over_ranks(statistics.median(comb_ms)) * 1e3
         bytes_per_step = sum_over_ranks(float(n_rows + combine_rows)) * args.hidden * 2
         nvlink_bytes = sum_over_ranks(float(recv_from_remote)) * args.hidden * 2  # dispatch direction only
         value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
-        # ---- end to end: pinned host inputs copied every step (overlapped on a copy stream), result read back
+        # ---- correctness of what was just timed (untimed): the routing counts against a host count of the
+        # gathered routing, every dispatched row against its source token, the round trip bit for bit
+        verified, verify_note = verify_round_trip(args, buf, rank, world, device, control_group, x, idx, w, expand)
+
+        # ---- end to end through the public API: every step copies its inputs from pinned host memory (on a copy
+        # stream, one step ahead) and reads its whole result, the combined [T, H] tokens, back into pinned host
+        # memory (on a second copy stream, overlapping the next step); the host touches each result once it is there
         e2e = None
         if not args.no_e2e:
-            copy_stream = torch.cuda.Stream()
+            up_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
             bufs = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
+            results_host = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
             h2d = hx.numel() * 2 + hidx.numel() * 8 + hw.numel() * 4
+            d2h = results_host[0].numel() * 2
 
             def upload(slot):
-                with torch.cuda.stream(copy_stream):
+                with torch.cuda.stream(up_stream):
                     for dst, src in zip(bufs[slot], (hx, hidx, hw)):
                         dst.copy_(src, non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record()
                 return ev
 
-            result_host = torch.empty(1, dtype=torch.float32).pin_memory()
             for phase, count in (("warm", 2), ("timed", args.steps)):
                 sync_all()
                 if phase == "timed":
                     clocks.__enter__()  # keep sampling clocks during the end-to-end timed region as well
                 t0 = time.perf_counter()
                 ready = upload(0)
+                landed = [None, None]
+                checksum = 0.0
                 for i in range(count):
                     slot = i & 1
                     nxt = upload(slot ^ 1) if i + 1 < count else None
@@ -354,11 +446,23 @@ def run_ours(args, rank, world, device, control_group):
                     # the comm stream waits for the copy through previous_event; the caller's stream too
                     torch.cuda.current_stream().wait_event(ready)
                     got, back = step(xd, idxd, wd, previous_event=ready)
-                    result_host.copy_(back.x.float().abs().mean().reshape(1), non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
-                    _ = float(result_host[0])
-                    copy_stream.wait_stream(torch.cuda.current_stream())
+                    done = torch.cuda.Event()
+                    done.record()
+                    if landed[slot] is not None:
+                        landed[slot].synchronize()  # the host buffer of step i-2 has been read below; its copy is long done
+                    with torch.cuda.stream(down_stream):
+                        down_stream.wait_event(done)
+                        results_host[slot].copy_(back.x, non_blocking=True)
+                        back.x.record_stream(down_stream)
+                        landed[slot] = torch.cuda.Event()
+                        landed[slot].record()
+                    up_stream.wait_event(done)  # the next upload into this slot's inputs must not overtake this step
+                    if i > 0:
+                        landed[slot ^ 1].synchronize()
+                        checksum += float(results_host[slot ^ 1][0, 0])  # the host reads the previous step's result
                     ready = nxt
+                landed[(count - 1) & 1].synchronize()
+                checksum += float(results_host[(count - 1) & 1][0, 0])
                 sync_all()
                 elapsed = time.perf_counter() - t0
             clocks.__exit__(None, None, None)
@@ -368,7 +472,8 @@ def run_ours(args, rank, world, device, control_group):
                 "unit": "GB/s",
                 "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4,
+                "d2h_bytes_per_step": d2h,
+                "read_back": "the whole combined [tokens, hidden] bf16 result of every step, into pinned host memory",
             }
         timed_wall_s = (ms_per_step + (e2e["ms_per_step"] if e2e else 0.0)) * 1e-3 * args.steps  # same value on every rank
         if timed_wall_s < 0.5:
@@ -386,6 +491,15 @@ def run_ours(args, rank, world, device, control_group):
         clock_summary = gather_clock_summaries(clocks.summary(), world, control_group)
         gc.enable()
 
+    # ---- same-box anchor: the NCCL all_to_all_single arm on the same inputs, same steps, same process
+    nccl = None
+    if not args.no_nccl_anchor:
+        try:
+            nccl_line = run_nccl(args, rank, world, device, control_group, sample_clocks=False)
+            nccl = {"ms_per_step": nccl_line["ms_per_step"], "dispatch_us": nccl_line["dispatch_us"], "combine_us": nccl_line["combine_us"]}
+        except Exception as error:  # the anchor must never cost the headline number
+            nccl = {"error": f"{type(error).__name__}: {error}"[:200]}
+
     line = {
         "metric": "ep_dispatch_combine_payload_GBps",
         "value": value,
@@ -396,7 +510,12 @@ def run_ours(args, rank, world, device, control_group):
         "ms_per_step": ms_per_step,
         "higher_is_better": True,
         "scaling": "weak",
-        "vs_baseline": None,
+        "vs_baseline": (nccl["ms_per_step"] / ms_per_step) if nccl and "ms_per_step" in nccl else None,
+        "vs_baseline_is": "this arm's steps per second / the NCCL all_to_all_single arm's, same inputs, same process, same box "
+                          "(the reference publishes no number for this configuration and does not install offline)",
+        "nccl_all_to_all": nccl,
+        "verified": verified,
+        "verify": verify_note,
         "dtype": "bf16",
         "data": "synthetic (seeded N(0,1) tokens, softmax top-k routing); no expert weights involved",
         "impl": "ours",
@@ -415,10 +534,12 @@ def run_ours(args, rank, world, device, control_group):
             "allow_multiple_reduction": args.multiple_reduction,
             "l2": f"inputs larger than L2: timed steps rotate over {len(x_sets)} copies of the token matrix ({len(x_sets) * x.numel() * 2 >> 20} MiB > 126 MB); a step also writes ~1 GB of outputs/window",
             "value_formula": "(sum_ranks N_dedup_rows + combine_rows) * hidden * 2 B / max_rank device time",
+            "value_uses": "mean: the sum of the timed steps' device times (max over ranks) / steps; step_ms_percentiles gives the spread",
             "host": "Python cyclic GC off inside the timed regions",
         },
         "dispatch_us": disp_us,
         "combine_us": comb_us,
+        "step_ms_percentiles": step_percentiles,
         "rows": {"recv_dedup": n_rows, "assignments": c_valid, "padded_capacity": c_padded},
         "nvlink_dispatch_GBps_per_gpu": (nvlink_bytes / world) / (disp_us * 1e-6) / 1e9 if world > 1 else 0.0,
         "wall_ms_per_step": max_over_ranks(wall * 1e3) / args.steps,
@@ -430,7 +551,7 @@ def run_ours(args, rank, world, device, control_group):
     return line
 
 
-def run_nccl(args, rank, world, device, control_group):
+def run_nccl(args, rank, world, device, control_group, sample_clocks=True):
     """Baseline: torch.distributed all_to_all_single over NCCL + index ops (sort, index_select, index_add)."""
     import torch
     import torch.distributed as dist
@@ -471,7 +592,7 @@ def run_nccl(args, rank, world, device, control_group):
         out.index_add_(0, token_of[order], returned.float())
         return out.to(x.dtype), mid, recv.shape[0]
 
-    clocks = ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid))
+    clocks = ClockSampler(device.index, str(torch.cuda.get_device_properties(device).uuid)) if sample_clocks else contextlib.nullcontext()
     for _ in range(args.warmup):
         dispatch_combine()
     torch.cuda.synchronize()
@@ -479,7 +600,8 @@ def run_nccl(args, rank, world, device, control_group):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     mids = []
-    clocks.wait_ready()
+    if sample_clocks:
+        clocks.wait_ready()
     with clocks:
         for i in range(args.steps):
             flush.fill_(i & 0xFF)
@@ -497,7 +619,7 @@ def run_nccl(args, rank, world, device, control_group):
     rows_t = torch.tensor([float(rows)], dtype=torch.float64)
     dist.all_reduce(rows_t, op=dist.ReduceOp.SUM, group=control_group)
     bytes_per_step = 2 * float(rows_t.item()) * H * 2
-    if ms_per_step * 1e-3 * args.steps < 0.5:
+    if sample_clocks and ms_per_step * 1e-3 * args.steps < 0.5:
         # too short for a clock record: repeat the same steps untimed with the sampling window open (same count on every rank)
         t0 = time.time()
         with clocks:
@@ -527,7 +649,7 @@ def run_nccl(args, rank, world, device, control_group):
         "dispatch_us": float(d.item()) * 1e3,
         "combine_us": (ms_per_step - float(d.item())) * 1e3,
         "gpu_launches": 0,
-        "clocks": gather_clock_summaries(clocks.summary(), world, control_group),
+        "clocks": gather_clock_summaries(clocks.summary(), world, control_group) if sample_clocks else None,
     }
 
 
@@ -565,9 +687,10 @@ def main():
         line = runner(args, rank, world, device, control)
         if rank == 0:
             print(json.dumps(line), flush=True)
+        failed = line.get("verified") is False
     finally:
         dist.destroy_process_group()
-    return 0
+    return 1 if failed else 0
 
 
 if __name__ == "__main__":

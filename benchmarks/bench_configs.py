@@ -37,7 +37,7 @@ def parse_args():
     p.add_argument("--impl", choices=("ours", "nccl"), default="ours")
     p.add_argument("--tokens", type=str, default="1,8,32,128,512,4096")
     p.add_argument("--fused", type=str, default="",
-                   help="decode/published: comma-separated dispatch_tokens:combine_tokens:blocks settings of the single-launch paths to "
+                   help="decode/published: comma-separated dispatch_tokens:blocks settings of the single-launch cached dispatch to "
                         "measure one after the other (empty: the library defaults)")
     return p.parse_args()
 
@@ -181,7 +181,7 @@ def main():
                             host_comb.append((h3 - h2) * 1e3)
                     buf.check_status()
                     rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H,
-                           "single_launch_limits": dict(zip(("dispatch_tokens", "combine_tokens", "blocks"), ext.fused_limits()))}
+                           "single_launch_limits": dict(zip(("dispatch_tokens", "blocks"), ext.fused_limits()))}
                     if args.config == "published":
                         # reference figure (single-node H20): NanoEP / DeepEP 2.1.0 microseconds
                         published = {2: (69.4, 40.2, 51.9), 4: (78.5, 54.9, 70.4), 8: (147.1, 91.8, 102.5)}.get(world)

@@ -28,10 +28,11 @@ py::dict layout_dict(const nep::WindowLayout& w) {
     d["routing_in_stride"] = w.routing_in_stride;
     d["stage_rows_offset"] = w.stage_rows_offset;
     d["stage_rows_stride"] = w.stage_rows_stride;
+    d["ret_parts"] = w.ret_parts;
+    d["rank_indexed"] = w.rank_indexed;
     d["ret_w_offset"] = w.ret_w_offset;
-    d["ret_w_stride"] = w.ret_w_stride;
+    d["ret_flag_offset"] = w.ret_flag_offset;
     d["ret_offset"] = w.ret_offset;
-    d["ret_stride"] = w.ret_stride;
     d["meta_scratch_offset"] = w.meta_scratch_offset;
     d["slot_scratch_offset"] = w.slot_scratch_offset;
     d["num_bytes"] = w.num_bytes;
@@ -45,16 +46,22 @@ py::dict layout_dict(const nep::WindowLayout& w) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "nanoep_b200 native runtime (sm_100a)";
 
-    m.def("window_layout", [](int ranks, int64_t max_tokens, int hidden, int topk, int64_t num_experts) {
-        return layout_dict(nep::WindowLayout::make(ranks, max_tokens, hidden, topk, num_experts));
-    });
+    m.def(
+        "window_layout",
+        [](int ranks, int64_t max_tokens, int hidden, int topk, int64_t num_experts, bool per_rank_reduction) {
+            return layout_dict(nep::WindowLayout::make(ranks, max_tokens, hidden, topk, num_experts, per_rank_reduction));
+        },
+        py::arg("ranks"), py::arg("max_tokens"), py::arg("hidden"), py::arg("topk"), py::arg("num_experts"),
+        py::arg("per_rank_reduction") = false);
 
     py::class_<PeerWindow>(m, "PeerWindow")
-        .def(py::init([](int rank, int world, int64_t max_tokens, int hidden, int topk, int64_t num_experts, double wait_timeout_s) {
-                 return new PeerWindow(rank, world, nep::WindowLayout::make(world, max_tokens, hidden, topk, num_experts), wait_timeout_s);
+        .def(py::init([](int rank, int world, int64_t max_tokens, int hidden, int topk, int64_t num_experts, double wait_timeout_s,
+                         bool per_rank_reduction) {
+                 return new PeerWindow(rank, world, nep::WindowLayout::make(world, max_tokens, hidden, topk, num_experts, per_rank_reduction),
+                                       wait_timeout_s);
              }),
              py::arg("rank"), py::arg("world"), py::arg("max_tokens"), py::arg("hidden"), py::arg("topk"), py::arg("num_experts"),
-             py::arg("wait_timeout_s") = 10.0)
+             py::arg("wait_timeout_s") = 10.0, py::arg("per_rank_reduction") = false)
         .def_property_readonly("rank", &PeerWindow::rank)
         .def_property_readonly("world", &PeerWindow::world)
         .def_property_readonly("device", &PeerWindow::device)
@@ -156,13 +163,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("num_sms"), py::arg("comm_stream"), py::arg("previous_event"), py::arg("async_op"));
 
     m.def("combine_finish", &nep::combine_finish);
-    m.def("next_combine_parity", [](PeerWindow& w) { return w.next_combine_parity(); });
     m.def("group_barrier", &nep::group_barrier);
     m.def("fused_limits", [] {
         const nep::FusedLimits f = nep::fused_limits();
-        return py::make_tuple(f.dispatch_tokens, f.combine_tokens, f.blocks);
+        return py::make_tuple(f.dispatch_tokens, f.blocks);
     });
-    m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("combine_tokens") = -1, py::arg("blocks") = -1);
+    m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1);
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });

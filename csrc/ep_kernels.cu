@@ -593,16 +593,23 @@ __device__ void pull_body(const PullParams& p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// push (combine): return expert outputs to the source ranks' partitions.  Tail = peer barrier.
+// combine: one launch.  Transfer warps return expert outputs to the source ranks' partitions and flag every
+// row on arrival; reduce warps sum a source token once all of its rows are flagged.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ char* ret_row(const CommonParams& c, int src, int parity, int part, int tok) {
+__device__ __forceinline__ char* ret_row(const CommonParams& c, int src, int part, int tok) {
     const WindowLayout& L = c.layout;
-    return window(c, src) + L.ret_offset + int64_t(parity) * L.ret_stride + (int64_t(part) * L.max_tokens + tok) * L.hidden * 2;
+    return window(c, src) + L.ret_offset + (int64_t(part) * L.max_tokens + tok) * L.hidden * 2;
 }
-__device__ __forceinline__ float* ret_w_row(const CommonParams& c, int src, int parity, int tok) {
+__device__ __forceinline__ float* ret_w_row(const CommonParams& c, int src, int tok) {
     const WindowLayout& L = c.layout;
-    return reinterpret_cast<float*>(window(c, src) + L.ret_w_offset + int64_t(parity) * L.ret_w_stride) + int64_t(tok) * L.topk;
+    return reinterpret_cast<float*>(window(c, src) + L.ret_w_offset) + int64_t(tok) * L.topk;
 }
+__device__ __forceinline__ uint32_t* ret_flag(const CommonParams& c, int src, int part, int tok) {
+    const WindowLayout& L = c.layout;
+    return reinterpret_cast<uint32_t*>(window(c, src) + L.ret_flag_offset) + int64_t(part) * L.max_tokens + tok;
+}
+// Value a combine writes into the arrival flags: never 0 (a fresh window), different for consecutive combines.
+__device__ __forceinline__ uint32_t combine_tag(uint64_t epoch) { return uint32_t(epoch % 0xffffffffull) + 1u; }
 
 __device__ __forceinline__ void accumulate8(float* acc, const int4& v) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -621,244 +628,339 @@ __device__ __forceinline__ int4 pack8(const float* acc) {
     return v;
 }
 
-// Returns true when the peer barrier succeeded (only meaningful to every block in fused mode).
-__device__ bool push_body(const PushParams& p) {
-    extern __shared__ __align__(128) char s_ring[];
+// Arrival flags of the two newest stores of a transfer warp.  A flag is published only after the bulk group
+// that carried its row has COMPLETED (cp.async.bulk.wait_group, not .read): two groups may stay in flight.
+struct FlagQueue {
+    uint32_t* older;
+    uint32_t* newer;
+    uint32_t tag;
+    __device__ __forceinline__ void publish(uint32_t* flag) const {
+        if ((threadIdx.x & 31) == 0 && flag != nullptr) {
+            fence_proxy_async();
+            st_release_sys_u32(flag, tag);
+        }
+    }
+    // Call right after committing the bulk group of the row that `flag` announces.
+    __device__ __forceinline__ void push(uint32_t* flag) {
+        bulk_wait_read<1>();  // the ring stage of the previous row may be refilled
+        bulk_wait<2>();       // the row before that has landed
+        __syncwarp();         // other lanes' gate-weight stores for that row are ordered before the flag
+        publish(older);
+        older = newer;
+        newer = flag;
+    }
+    __device__ __forceinline__ void drain() {
+        bulk_wait<0>();
+        __syncwarp();
+        publish(older);
+        publish(newer);
+        older = newer = nullptr;
+    }
+};
+
+// Transfer warps.  Receive rows are visited round-robin over the source ranks (SourceWalk), so at every moment
+// the warps of a GPU address all destinations evenly; a row of the expert-major layout yields one transfer per
+// local slot.
+__device__ void combine_push_role(const CombineParams& p, char* smem) {
     const WindowLayout& L = p.c.layout;
     const int R = L.ranks, K = L.topk, H = L.hidden;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-    const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, PW = p.push_warps;
+    const int gw = blockIdx.x * PW + warp, GW = gridDim.x * PW;
     const StatusRef status = status_of(p.c);
     const int MW = K + 2;
     const uint32_t xb = uint32_t(H) * 2u;
-    Ring ring = make_ring(s_ring, wpb, p.stages, xb);
+    Ring ring = make_ring(smem, PW, p.stages, xb);
     const int S = p.stages;
-    int* ctrl = ctrl_words(p.c);
-
-    auto checked_source = [&](const int* m, int item, int& src, int& tok) {
-        src = m[0];
-        tok = m[1];
-        if (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens) {
-            if (lane == 0) report(status, kBadMetadata, uint32_t(item), kTagPush);
-            return false;
-        }
-        return true;
-    };
+    const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
+    const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
+    FlagQueue flags{nullptr, nullptr, combine_tag(p.epoch)};
 
     if (p.mode == kPushExpandedReduce) {
         // FP32 sum of the row's local slots, one bf16 round, one store per (token, this rank).
         const int vecs = H / 8;
-        const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
-        const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
+        int q = 0;  // rows sent so far: consecutive rows use consecutive ring stages
         for (int i = 0; i < n_my; ++i) {
             int r;
             const bool live_row = walk.locate(gw + i * GW, r);
             const int* m = p.meta + int64_t(live_row ? r : 0) * MW;
             const int v = (live_row && lane < K) ? m[2 + lane] : -1;
             const unsigned vm = __ballot_sync(kFull, v >= 0 && v < p.capacity);
-            int src = 0, tok = 0;
-            const bool fine = live_row && checked_source(m, r, src, tok) && vm != 0;
-            char* st = ring.slot(i);
-            if (fine) {
-                // four 16-byte column chunks x two slots per step: eight independent loads per lane in flight
-                for (int c0 = lane; c0 < vecs; c0 += 128) {
-                    float acc[4][8];
+            const int src = m[0], tok = m[1];
+            bool fine = live_row && vm != 0;
+            if (fine && (src < 0 || src >= R || tok < 0 || tok >= L.max_tokens || __any_sync(kFull, v >= p.capacity))) {
+                if (lane == 0) report(status, kBadMetadata, uint32_t(r), kTagPush);
+                fine = false;
+            }
+            if (!fine) continue;
+            char* st = ring.slot(q++);
+            // four 16-byte column chunks x two slots per step: eight independent loads per lane in flight
+            for (int c0 = lane; c0 < vecs; c0 += 128) {
+                float acc[4][8];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 4; ++u)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
-                    unsigned left = vm;
-                    while (left) {
-                        const int k0 = __ffs(left) - 1;
-                        left &= left - 1;
-                        const int k1 = left ? __ffs(left) - 1 : -1;
-                        if (left) left &= left - 1;
-                        const int slot0 = __shfl_sync(kFull, v, k0);
-                        const int slot1 = __shfl_sync(kFull, v, k1 < 0 ? 0 : k1);
-                        const int4* r0 = reinterpret_cast<const int4*>(p.y + int64_t(slot0) * H);
-                        const int4* r1 = reinterpret_cast<const int4*>(p.y + int64_t(slot1) * H);
-                        int4 d0[4], d1[4];
+                    for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+                unsigned left = vm;
+                while (left) {
+                    const int k0 = __ffs(left) - 1;
+                    left &= left - 1;
+                    const int k1 = left ? __ffs(left) - 1 : -1;
+                    if (left) left &= left - 1;
+                    const int slot0 = __shfl_sync(kFull, v, k0);
+                    const int slot1 = __shfl_sync(kFull, v, k1 < 0 ? 0 : k1);
+                    const int4* r0 = reinterpret_cast<const int4*>(p.y + int64_t(slot0) * H);
+                    const int4* r1 = reinterpret_cast<const int4*>(p.y + int64_t(slot1) * H);
+                    int4 d0[4], d1[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (c0 + 32 * u < vecs) {
-                                d0[u] = ld_nc_v4(r0 + c0 + 32 * u);
-                                if (k1 >= 0) d1[u] = ld_nc_v4(r1 + c0 + 32 * u);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (c0 + 32 * u < vecs) {
-                                accumulate8(acc[u], d0[u]);
-                                if (k1 >= 0) accumulate8(acc[u], d1[u]);
-                            }
+                    for (int u = 0; u < 4; ++u) {
+                        if (c0 + 32 * u < vecs) {
+                            d0[u] = ld_nc_v4(r0 + c0 + 32 * u);
+                            if (k1 >= 0) d1[u] = ld_nc_v4(r1 + c0 + 32 * u);
                         }
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (c0 + 32 * u < vecs) reinterpret_cast<int4*>(st)[c0 + 32 * u] = pack8(acc[u]);
+                    for (int u = 0; u < 4; ++u) {
+                        if (c0 + 32 * u < vecs) {
+                            accumulate8(acc[u], d0[u]);
+                            if (k1 >= 0) accumulate8(acc[u], d1[u]);
+                        }
+                    }
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                const int part = __ffs(vm) - 1;
-                if (lane == 0) bulk_store(ret_row(p.c, src, p.parity, part, tok), st, xb);
-                if (p.w != nullptr && ((vm >> lane) & 1u)) st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + lane, p.w[v]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (c0 + 32 * u < vecs) reinterpret_cast<int4*>(st)[c0 + 32 * u] = pack8(acc[u]);
             }
-            bulk_commit();
-            if (S > 1) bulk_wait_read<1>(); else bulk_wait_read<0>();
+            fence_proxy_async_smem();
             __syncwarp();
+            const int part = L.rank_indexed ? p.c.rank : __ffs(vm) - 1;
+            if (lane == 0) bulk_store(ret_row(p.c, src, part, tok), st, xb);
+            if (p.w != nullptr && ((vm >> lane) & 1u)) st_relaxed_sys_f32(ret_w_row(p.c, src, tok) + lane, p.w[v]);
+            bulk_commit();
+            flags.push(ret_flag(p.c, src, part, tok));
         }
-    } else {
-        // One bulk load + one bulk store per item (compact: receive row; expanded: slot).
-        // Expanded: walk the slots (sources are interleaved by the plan's arrival order).
-        // Compact: walk the receive rows round-robin over the sources.
-        const bool by_slot = p.mode == kPushExpanded;
-        const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
-        const int items = by_slot ? p.capacity : walk.items;
-        const int n_my = items > gw ? (items - gw + GW - 1) / GW : 0;
-        // item index -> (live?, y row to send)
-        auto locate = [&](int v, int& item) {
+        flags.drain();
+        return;
+    }
+
+    // One bulk load + one bulk store per transfer.  A cursor enumerates the transfers of this warp's rows:
+    // compact layout = one per receive row; expert-major layout = one per local slot of the row.
+    const bool by_slot = p.mode == kPushExpanded;
+    struct Cursor {
+        int i;          // position in this warp's row sequence
+        unsigned left;  // choices of the current row that still need a transfer
+        unsigned vm;    // all valid choices of the current row
+        int r, v, src, tok, k;
+    };
+    auto next = [&](Cursor& c) {
+        while (c.left == 0) {
+            if (++c.i >= n_my) return false;
+            int r;
+            if (!walk.locate(gw + c.i * GW, r)) continue;
+            const int* m = p.meta + int64_t(r) * MW;
+            c.r = r;
+            c.src = m[0];
+            c.tok = m[1];
+            c.v = lane < K ? m[2 + lane] : -1;
+            c.vm = __ballot_sync(kFull, c.v >= 0);
+            const bool bad_slot = __any_sync(kFull, by_slot && c.v >= p.capacity);
+            if (c.src < 0 || c.src >= R || c.tok < 0 || c.tok >= L.max_tokens || bad_slot) {
+                if (lane == 0) report(status, kBadMetadata, uint32_t(r), kTagPush);
+                c.vm = 0;
+            }
+            c.left = by_slot ? c.vm : (c.vm & (0u - c.vm));  // compact: the first valid choice names the partition
+        }
+        c.k = __ffs(c.left) - 1;
+        c.left &= c.left - 1;
+        return true;
+    };
+    auto issue = [&](const Cursor& c, int q) {
+        const int y_row = by_slot ? __shfl_sync(kFull, c.v, c.k) : c.r;
+        if (lane == 0) {
+            mbar_expect_tx(ring.bar(q), xb);
+            bulk_load(ring.slot(q), p.y + int64_t(y_row) * H, xb, ring.bar(q));
+        }
+    };
+    Cursor ahead{-1, 0u, 0u, 0, -1, 0, 0, 0}, now{-1, 0u, 0u, 0, -1, 0, 0, 0};
+    int issued = 0;
+    bool more = true;
+    while (issued < S - 1 && (more = next(ahead))) issue(ahead, issued++);
+    for (int q = 0; next(now); ++q) {
+        if (!ring.wait(q, p.c.timeout_ns)) {
+            if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
+            break;
+        }
+        const int part = by_slot ? now.k : (L.rank_indexed ? p.c.rank : now.k);
+        if (lane == 0) bulk_store(ret_row(p.c, now.src, part, now.tok), ring.slot(q), xb);
+        if (p.w != nullptr) {
             if (by_slot) {
-                item = v;
-                return p.slot_map[v] >= 0;
+                const int slot = __shfl_sync(kFull, now.v, now.k);
+                if (lane == 0) st_relaxed_sys_f32(ret_w_row(p.c, now.src, now.tok) + now.k, p.w[slot]);
+            } else if ((now.vm >> lane) & 1u) {
+                st_relaxed_sys_f32(ret_w_row(p.c, now.src, now.tok) + lane, p.w[int64_t(now.r) * K + lane]);
             }
-            return walk.locate(v, item);
-        };
-        auto issue = [&](int i) {
-            int item;
-            const bool live = locate(gw + i * GW, item);
-            if (lane == 0 && live) {
-                mbar_expect_tx(ring.bar(i), xb);
-                bulk_load(ring.slot(i), p.y + int64_t(item) * H, xb, ring.bar(i));
-            }
-        };
-        for (int i = 0; i < min(S - 1, n_my); ++i) issue(i);
-        for (int i = 0; i < n_my; ++i) {
-            int item;
-            if (locate(gw + i * GW, item)) {
-                if (!ring.wait(i, p.c.timeout_ns)) {
-                    if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
-                    break;
-                }
-                int r = item, k_of_slot = 0;
-                if (by_slot) {
-                    const int a = p.slot_map[item];
-                    r = a / K;
-                    k_of_slot = a % K;
-                }
-                int src = 0, tok = 0;
-                const bool in_range = r >= 0 && r < p.rows;
-                const int* m = p.meta + int64_t(in_range ? r : 0) * MW;
-                if (!in_range && lane == 0) report(status, kBadMetadata, uint32_t(item), kTagPush);
-                if (in_range && checked_source(m, item, src, tok)) {
-                    if (by_slot) {
-                        if (lane == 0) {
-                            bulk_store(ret_row(p.c, src, p.parity, k_of_slot, tok), ring.slot(i), xb);
-                            if (p.w != nullptr) st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + k_of_slot, p.w[item]);
-                        }
-                    } else {
-                        const int v = lane < K ? m[2 + lane] : -1;
-                        const unsigned vm = __ballot_sync(kFull, v >= 0);
-                        if (vm != 0) {
-                            if (lane == 0) bulk_store(ret_row(p.c, src, p.parity, __ffs(vm) - 1, tok), ring.slot(i), xb);
-                            if (p.w != nullptr && v >= 0)
-                                st_relaxed_sys_f32(ret_w_row(p.c, src, p.parity, tok) + lane, p.w[int64_t(r) * K + lane]);
-                        }
-                    }
-                }
-            }
-            bulk_commit();
-            bulk_wait_read<1>();
-            __syncwarp();
-            if (i + S - 1 < n_my) issue(i + S - 1);
         }
+        bulk_commit();
+        flags.push(ret_flag(p.c, now.src, part, now.tok));
+        if (more && (more = next(ahead))) issue(ahead, issued++);
     }
-    bulk_wait<0>();
+    flags.drain();
+}
+
+// Which return partitions hold a row for source token `t`, as a mask over the lanes (choices) that name them;
+// `valid` is the lane's own choice.  One partition per valid choice, or one per destination rank (named by
+// the rank's first choice).
+__device__ __forceinline__ unsigned expected_parts(const int64_t* topk, int t, int K, int E, int Le, bool sum_all_choices, bool& valid,
+                                                   int& dest) {
+    const int lane = threadIdx.x & 31;
+    const int64_t e = lane < K ? topk[int64_t(t) * K + lane] : -1;
+    valid = e >= 0 && e < E;
+    dest = valid ? int(e) / Le : -1;
+    const unsigned vmask = __ballot_sync(kFull, valid);
+    if (sum_all_choices) return vmask;
+    bool leader = false;
+    if (valid) {
+        const unsigned same = __match_any_sync(vmask, dest);
+        leader = lane == __ffs(same) - 1;
+    }
+    return __ballot_sync(kFull, leader);
+}
+
+// FP32 sum of the partitions in `parts` (ascending choice order), optional bias once, one bf16 round.
+__device__ __forceinline__ void reduce_token(const CommonParams& c, int t, unsigned parts, int my_part, const __nv_bfloat16* bias,
+                                             __nv_bfloat16* out) {
+    const WindowLayout& L = c.layout;
+    const int H = L.hidden, lane = threadIdx.x & 31;
+    const int vecs = H / 8;
+    const int64_t part_stride = L.max_tokens * int64_t(H) * 2;
+    const char* row0 = window(c, c.rank) + L.ret_offset + int64_t(t) * H * 2;
+    for (int col = lane; col < vecs; col += 64) {
+        const bool two = col + 32 < vecs;
+        float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        unsigned left = parts;
+        while (left) {
+            int part[4];
+            int4 d0[4], d1[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = left ? __ffs(left) - 1 : -1;
+                if (left) left &= left - 1;
+                part[j] = __shfl_sync(kFull, my_part, k < 0 ? 0 : k);
+                if (k < 0) part[j] = -1;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (part[j] >= 0) {
+                    const int4* src = reinterpret_cast<const int4*>(row0 + part[j] * part_stride);
+                    d0[j] = ld_cg_v4(src + col);
+                    if (two) d1[j] = ld_cg_v4(src + col + 32);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (part[j] >= 0) {
+                    accumulate8(a0, d0[j]);
+                    if (two) accumulate8(a1, d1[j]);
+                }
+            }
+        }
+        if (bias != nullptr) {
+            const int4* b = reinterpret_cast<const int4*>(bias + int64_t(t) * H);
+            accumulate8(a0, ld_nc_v4(b + col));
+            if (two) accumulate8(a1, ld_nc_v4(b + col + 32));
+        }
+        int4* o = reinterpret_cast<int4*>(out + int64_t(t) * H);
+        o[col] = pack8(a0);
+        if (two) o[col + 32] = pack8(a1);
+    }
+}
+
+// Reduce warps of the combine kernel: token t is summed once every partition it expects carries this combine's tag.
+__device__ void combine_reduce_role(const CombineParams& p) {
+    const WindowLayout& L = p.c.layout;
+    const int K = L.topk, Le = L.local_experts, E = int(L.num_experts);
+    const int lane = threadIdx.x & 31;
+    const int RW = (blockDim.x >> 5) - p.push_warps;
+    const int gw = blockIdx.x * RW + ((threadIdx.x >> 5) - p.push_warps), GW = gridDim.x * RW;
+    const StatusRef status = status_of(p.c);
+    const uint32_t tag = combine_tag(p.epoch);
+    const uint32_t* flag_base = reinterpret_cast<const uint32_t*>(window(p.c, p.c.rank) + L.ret_flag_offset);
+    const float* ret_w = reinterpret_cast<const float*>(window(p.c, p.c.rank) + L.ret_w_offset);
+    for (int t = gw; t < p.tokens; t += GW) {
+        bool valid;
+        int dest;
+        const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
+        const int my_part = L.rank_indexed ? dest : lane;
+        const bool mine = (parts >> lane) & 1u;
+        if (parts != 0) {
+            const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
+            const uint64_t start = global_timer_ns();
+            uint32_t spins = 0;
+            bool arrived = false;
+            for (;;) {
+                const bool here = !mine || ld_acquire_sys_u32(flag) == tag;
+                arrived = __all_sync(kFull, here);
+                if (arrived) break;
+                __nanosleep(100);
+                if ((++spins & 15u) == 0u && __any_sync(kFull, global_timer_ns() - start > p.c.timeout_ns)) break;
+            }
+            __syncwarp();
+            if (!arrived) {
+                if (lane == 0) report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
+                return;  // a peer never delivered: stop reducing, the host reports the status
+            }
+        }
+        reduce_token(p.c, t, parts, my_part, p.bias, p.out);
+        if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+    }
+}
+
+__device__ void combine_body(const CombineParams& p) {
+    extern __shared__ __align__(128) char s_ring[];
+    __shared__ int s_enter;
+    const WindowLayout& L = p.c.layout;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const StatusRef status = status_of(p.c);
+    int* ctrl = ctrl_words(p.c);
+    if (threadIdx.x == 0) s_enter = 1;
+    __syncthreads();
+    if (p.wait_epoch != 0) {
+        // Every peer has finished reading what the previous combine left in its return area.
+        if (warp == 0) {
+            const bool ok = peer_wait_warp(p.c.peers, p.c.rank, L.ranks, L.signal_offset, p.wait_epoch, p.c.timeout_ns, status, kTagPush);
+            if (lane == 0) s_enter = ok;
+        }
+        __syncthreads();
+    }
+    if (s_enter) {
+        if (warp < p.push_warps)
+            combine_push_role(p, s_ring);
+        else
+            combine_reduce_role(p);
+    }
+    // The last block out tells every peer that this rank is done with the combine (nobody waits here).
     __threadfence_system();
-    if (!take_last_ticket(ctrl + WindowLayout::kTicketPush)) {
-        if (!p.fused) return false;
-        return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagPush);
-    }
-    if (threadIdx.x == 0) ctrl[WindowLayout::kTicketPush] = 0;
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketCombine)) return;
+    if (threadIdx.x == 0) ctrl[WindowLayout::kTicketCombine] = 0;
     __threadfence_system();
     __syncthreads();
-    __shared__ int s_ok;
-    if (warp == 0) {
-        const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagPush);
-        if (lane == 0) s_ok = ok;
-    }
-    __syncthreads();
-    if (p.fused && threadIdx.x == 0) publish_go(ctrl, p.epoch, s_ok != 0);
-    return s_ok != 0;
+    if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, L.ranks, L.signal_offset, p.epoch);
 }
 
 // ------------------------------------------------------------------------------------------
-// reduce (combine): per source token, FP32 sum of the partitions that were written for it,
-// optional bias once, one bf16 round; gate-weight payload restored with masked choices = 0.
+// reduce alone: source-side sum of rows that another kernel pushed and a peer barrier made visible.
 // ------------------------------------------------------------------------------------------
 __device__ void reduce_body(const ReduceParams& p) {
     const WindowLayout& L = p.c.layout;
-    const int K = L.topk, H = L.hidden, Le = L.local_experts;
-    const int E = int(L.num_experts);
+    const int K = L.topk, Le = L.local_experts, E = int(L.num_experts);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     const int gw = blockIdx.x * wpb + warp, GW = gridDim.x * wpb;
-    const char* win = window(p.c, p.c.rank);
-    const char* ret = win + L.ret_offset + int64_t(p.parity) * L.ret_stride;
-    const float* ret_w = reinterpret_cast<const float*>(win + L.ret_w_offset + int64_t(p.parity) * L.ret_w_stride);
-    const int vecs = H / 8;
-    const int64_t part_stride = L.max_tokens * int64_t(H) * 2;
-
+    const float* ret_w = reinterpret_cast<const float*>(window(p.c, p.c.rank) + L.ret_w_offset);
     for (int t = gw; t < p.tokens; t += GW) {
-        const int64_t e = lane < K ? p.topk[int64_t(t) * K + lane] : -1;
-        const bool valid = e >= 0 && e < E;
-        const unsigned vmask = __ballot_sync(kFull, valid);
-        unsigned parts = vmask;
-        if (!p.sum_all_choices) {
-            bool leader = false;
-            if (valid) {
-                const unsigned same = __match_any_sync(vmask, int(e) / Le);
-                leader = lane == __ffs(same) - 1;
-            }
-            parts = __ballot_sync(kFull, leader);
-        }
-        const char* row0 = ret + int64_t(t) * H * 2;
-        for (int c = lane; c < vecs; c += 64) {
-            const bool two = c + 32 < vecs;
-            float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            unsigned left = parts;
-            while (left) {
-                int k[4];
-                int4 d0[4], d1[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    k[j] = left ? __ffs(left) - 1 : -1;
-                    if (left) left &= left - 1;
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (k[j] >= 0) {
-                        const int4* src = reinterpret_cast<const int4*>(row0 + k[j] * part_stride);
-                        d0[j] = ld_cg_v4(src + c);
-                        if (two) d1[j] = ld_cg_v4(src + c + 32);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (k[j] >= 0) {
-                        accumulate8(a0, d0[j]);
-                        if (two) accumulate8(a1, d1[j]);
-                    }
-                }
-            }
-            if (p.bias != nullptr) {
-                const int4* b = reinterpret_cast<const int4*>(p.bias + int64_t(t) * H);
-                accumulate8(a0, ld_nc_v4(b + c));
-                if (two) accumulate8(a1, ld_nc_v4(b + c + 32));
-            }
-            int4* out = reinterpret_cast<int4*>(p.out + int64_t(t) * H);
-            out[c] = pack8(a0);
-            if (two) out[c + 32] = pack8(a1);
-        }
+        bool valid;
+        int dest;
+        const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
+        reduce_token(p.c, t, parts, L.rank_indexed ? dest : lane, p.bias, p.out);
         if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
     }
 }
@@ -967,8 +1069,8 @@ __global__ void __launch_bounds__(kStageThreads) stage_kernel(const __grid_const
 __global__ void __launch_bounds__(kStageThreads) stage_multi_kernel(const StageParams* all) { stage_body(all[blockIdx.y]); }
 NEP_KERNEL_PAIR(plan, PlanParams, kPlanThreads)
 NEP_KERNEL_PAIR(pull, PullParams, 256)
-__global__ void __launch_bounds__(256) push_kernel(const __grid_constant__ PushParams p) { push_body(p); }
-__global__ void __launch_bounds__(256) push_multi_kernel(const PushParams* all) { push_body(all[blockIdx.y]); }
+__global__ void __launch_bounds__(kCombineThreads, 1) combine_kernel(const __grid_constant__ CombineParams p) { combine_body(p); }
+__global__ void __launch_bounds__(kCombineThreads, 1) combine_multi_kernel(const CombineParams* all) { combine_body(all[blockIdx.y]); }
 NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
 NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
 NEP_KERNEL_PAIR(local_combine, LocalCombineParams, kReduceThreads)
@@ -983,16 +1085,6 @@ __global__ void __launch_bounds__(256) fused_cached_dispatch_multi_kernel(const 
     if (!stage_body(sp[blockIdx.y])) return;
     fence_proxy_async();
     pull_body(pp[blockIdx.y]);
-}
-
-// push + peer barrier + reduce in one cooperative launch (small combines)
-__global__ void __launch_bounds__(256) fused_combine_kernel(const __grid_constant__ PushParams pp, const __grid_constant__ ReduceParams rp) {
-    if (!push_body(pp)) return;
-    reduce_body(rp);
-}
-__global__ void __launch_bounds__(256) fused_combine_multi_kernel(const PushParams* pp, const ReduceParams* rp) {
-    if (!push_body(pp[blockIdx.y])) return;
-    reduce_body(rp[blockIdx.y]);
 }
 
 template <typename Params>
@@ -1055,9 +1147,6 @@ cudaError_t launch_plan(const PlanParams* params, LaunchShape shape, size_t smem
 cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream) {
     return launch_pair<PullParams>(pull_kernel, pull_multi_kernel, params, shape, warps * 32, smem, stream);
 }
-cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream) {
-    return launch_pair<PushParams>(push_kernel, push_multi_kernel, params, shape, warps * 32, smem, stream);
-}
 cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream) {
     return launch_pair<ReduceParams>(reduce_kernel, reduce_multi_kernel, params, shape, kReduceThreads, 0, stream);
 }
@@ -1097,11 +1186,24 @@ cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullPar
                               warps, smem, stream, granted);
 }
 
-cudaError_t launch_fused_combine(const PushParams* push, const ReduceParams* reduce, LaunchShape shape, int warps, size_t smem,
-                                 cudaStream_t stream) {
+cudaError_t launch_combine(const CombineParams* params, LaunchShape shape, size_t smem, cudaStream_t stream, bool cooperative) {
+    if (!cooperative) return launch_pair<CombineParams>(combine_kernel, combine_multi_kernel, params, shape, kCombineThreads, smem, stream);
+    const bool multi = shape.ranks_y > 1;
+    const void* fn = multi ? (const void*)combine_multi_kernel : (const void*)combine_kernel;
     static thread_local size_t granted[2][64] = {};
-    return launch_cooperative((const void*)fused_combine_kernel, (const void*)fused_combine_multi_kernel, push, reduce, shape, warps, smem,
-                              stream, granted);
+    if (smem > 48 * 1024) {
+        int device = 0;
+        cudaGetDevice(&device);
+        size_t& have = granted[multi ? 1 : 0][device & 63];
+        if (smem > have) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return e;
+            have = smem;
+        }
+    }
+    const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
+    void* args[1] = {multi ? (void*)&params : (void*)params};
+    return cudaLaunchCooperativeKernel(fn, grid, dim3(kCombineThreads), args, smem, stream);
 }
 
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream) {
@@ -1115,9 +1217,8 @@ int kernel_table(KernelInfo* out, int capacity) {
     };
     const Entry entries[] = {
         {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
-        {"push", (const void*)push_kernel},     {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
+        {"combine", (const void*)combine_kernel}, {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
         {"local_combine", (const void*)local_combine_kernel}, {"fused_cached_dispatch", (const void*)fused_cached_dispatch_kernel},
-        {"fused_combine", (const void*)fused_combine_kernel},
     };
     int n = 0;
     for (const Entry& e : entries) {

@@ -10,8 +10,9 @@
 //              -> plan (fresh only: receivers scan the sources' routing and assign rows/slots)
 //              -> pull (receivers bulk-load rows from the sources' windows straight into the
 //                 final compact / expert-major output, zero padding included)
-//   combine  = push (expert ranks bulk-store result rows into the sources' return partitions,
-//              optional FP32 local pre-reduction, peer barrier) -> reduce (source-side FP32 sum).
+//   combine  = ONE kernel: transfer warps bulk-store result rows into the sources' return partitions
+//              (optional FP32 local pre-reduction) and flag each row on arrival; reduce warps of the
+//              same launch sum a source token as soon as all of its rows are flagged.
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -86,22 +87,36 @@ struct PullParams {
 
 enum PushMode : int { kPushCompact = 0, kPushExpanded = 1, kPushExpandedReduce = 2 };
 
-struct PushParams {
+// One launch per combine.  Every CTA holds `push_warps` transfer warps (shared-memory ring, bulk copies) and
+// reduce warps.  Transfer warps return this rank's expert outputs to the source ranks' return partitions and,
+// once a row's bulk store has completed, publish the combine's tag in the row's arrival flag.  Reduce warps
+// walk this rank's own source tokens, wait (bounded) until every partition a token expects carries the tag,
+// and write the FP32 sum.  No barrier sits between the two: the only cross-rank waits are the flags.
+struct CombineParams {
     CommonParams c;
+    // expert side
     const __nv_bfloat16* y;  // [N,H] or [C,H]
     const float* w;          // [N,K] or [C] or null
     const int* meta;         // [N,K+2]
-    const int* slot_map;     // [C] (expanded)
     const int64_t* recv_rank_prefix;  // [R] inclusive receive rows by source
     int rows;                // N
     int capacity;            // C
-    int mode;
-    int parity;
+    int mode;                // PushMode
     int stages;
-    int fused;               // 1: every block waits for the peer barrier's outcome (single-launch combine)
-    uint64_t epoch;
+    int push_warps;
+    // source side
+    const int64_t* topk;           // [T,K] source routing snapshot
+    const __nv_bfloat16* bias;     // [T,H] or null
+    __nv_bfloat16* out;            // [T,H]
+    float* w_out;                  // [T,K] or null
+    int tokens;
+    int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank
+    uint64_t epoch;       // signalled to every peer when this rank's pushes and reduction are done
+    uint64_t wait_epoch;  // peers must have signalled this much before their return area is overwritten (0: nothing to wait for)
 };
 
+// Source-side reduction alone, for a combine whose rows were pushed by another kernel (the scatter epilogue of
+// the down-projection GEMM) and made visible by a peer barrier.
 struct ReduceParams {
     CommonParams c;
     const int64_t* topk;           // [T,K] source routing snapshot
@@ -109,8 +124,7 @@ struct ReduceParams {
     __nv_bfloat16* out;            // [T,H]
     float* w_out;                  // [T,K] or null
     int tokens;
-    int parity;
-    int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank (first k)
+    int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank
 };
 
 // Single-rank combine: every contribution is local, so the expert outputs are summed straight into
@@ -144,16 +158,14 @@ struct LaunchShape {
 cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
 cudaError_t launch_plan(const PlanParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
 cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
-cudaError_t launch_push(const PushParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
+// `cooperative`: every block must be resident at once (a whole logical group in one launch waits on itself).
+cudaError_t launch_combine(const CombineParams* params, LaunchShape shape, size_t smem, cudaStream_t stream, bool cooperative);
 cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream);
 cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaStream_t stream);
 // Cached dispatch for small calls: stage, peer barrier and pull in ONE cooperative launch (all blocks
 // resident; the block that finishes staging last runs the barrier and releases the others).
 cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
                                          cudaStream_t stream);
-// push + peer barrier + reduce in one cooperative launch (small combines)
-cudaError_t launch_fused_combine(const PushParams* push, const ReduceParams* reduce, LaunchShape shape, int warps, size_t smem,
-                                 cudaStream_t stream);
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream);
 
 // Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.
@@ -162,6 +174,7 @@ struct RingPlan {
     size_t smem_bytes;
 };
 RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes);
+constexpr int kCombineThreads = 512;  // transfer warps + reduce warps of one combine CTA
 int stage_smem_bytes(const WindowLayout& l);
 int plan_smem_bytes(const WindowLayout& l);
 

@@ -141,10 +141,12 @@ void bind_gemm(pybind11::module_& m) {
         pybind11::arg("stages") = 4, pybind11::arg("pair") = false);
 
     // Down projection fused with the combine push: row r of (A @ W[e]^T) * slot_weight[r] is stored
-    // (bf16) into the return partition of the row's source rank; padding rows are skipped.
+    // (bf16) into the return partition of the row's source rank; padding rows are skipped.  The return area
+    // exists once: a dispatch (whose peer barrier every rank passes only after its previous reduction) must lie
+    // between two such calls, as it does in a layer's forward pass.
     m.def(
         "grouped_gemm_scatter",
-        [](PeerWindow& window, int64_t parity, const at::Tensor& a, const at::Tensor& w, const at::Tensor& expert_offsets,
+        [](PeerWindow& window, const at::Tensor& a, const at::Tensor& w, const at::Tensor& expert_offsets,
            const at::Tensor& slot_map, const at::Tensor& recv_metadata, c10::optional<at::Tensor> slot_weights, at::Tensor& status,
            int64_t max_ctas, double timeout_s, bool pair) {
             c10::cuda::CUDAGuard guard(a.device());
@@ -165,7 +167,8 @@ void bind_gemm(pybind11::module_& m) {
             }
             const CommonParams c = window.common();
             for (int p = 0; p < kMaxRanks; ++p) g.args.peers[p] = c.peers[p];
-            g.args.ret_offset = L.ret_offset + parity * L.ret_stride;
+            TORCH_CHECK(L.ret_parts == L.topk, "the fused combine epilogue needs one return partition per choice (allow_multiple_reduction=False)");
+            g.args.ret_offset = L.ret_offset;
             g.args.max_tokens = L.max_tokens;
             g.args.topk = L.topk;
             g.args.ranks = L.ranks;
@@ -184,7 +187,7 @@ void bind_gemm(pybind11::module_& m) {
             }
             TORCH_CHECK(e == cudaSuccess, "grouped GEMM (scatter) launch failed: ", cudaGetErrorString(e));
         },
-        pybind11::arg("window"), pybind11::arg("parity"), pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"),
+        pybind11::arg("window"), pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("expert_offsets"),
         pybind11::arg("slot_map"), pybind11::arg("recv_metadata"), pybind11::arg("slot_weights"), pybind11::arg("status"),
         pybind11::arg("max_ctas") = 0, pybind11::arg("timeout_s") = 5.0, pybind11::arg("pair") = true);
 

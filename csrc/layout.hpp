@@ -3,9 +3,12 @@
 // One header shared by host and device code so both sides compute identical offsets.  The
 // reference keeps the same "single source of truth" idea in csrc/layout.hpp:59-98, but the
 // regions here serve a different protocol: senders *stage* their tokens in their own window
-// and receivers pull them, every remotely accessed region exists twice (parity = operation
-// sequence & 1) so that one peer barrier per operation is enough, and the combine return
-// area is a [K partitions][Tmax] array written by the expert ranks.
+// and receivers pull them; the dispatch regions that peers touch exist twice (parity = dispatch
+// sequence & 1) so that one peer barrier per dispatch is enough; the combine return area is a
+// single [P partitions][Tmax] array written by the expert ranks, with one arrival flag per
+// (partition, token) that carries the writing operation's tag.  P = K, or min(R, K) when the
+// buffer pre-reduces per rank (the reference sizes its return area the same way,
+// csrc/layout.hpp:51-57).
 #pragma once
 #include <cstdint>
 #include <stdexcept>
@@ -46,17 +49,18 @@ struct WindowLayout {
     int64_t routing_in_stride;
     int64_t stage_rows_offset;   // [2] u8[Tmax][wire_row_bytes] staged tokens, pulled by the receivers
     int64_t stage_rows_stride;
-    int64_t ret_w_offset;        // [2] f32[Tmax][K] gate-weight payload returned by combine
-    int64_t ret_w_stride;
-    int64_t ret_offset;          // [2] bf16[K][Tmax][H] expert outputs pushed back by combine
-    int64_t ret_stride;
+    int ret_parts;               // P: return partitions per token
+    int rank_indexed;            // 1: partition = expert rank (P == R); 0: partition = index of the choice
+    int64_t ret_w_offset;        // f32[Tmax][K] gate-weight payload returned by combine
+    int64_t ret_flag_offset;     // u32[P][Tmax] tag of the combine that last wrote (partition, token)
+    int64_t ret_offset;          // bf16[P][Tmax][H] expert outputs pushed back by combine
     int64_t meta_scratch_offset; // i32[R*Tmax][K+2] receive plan of a fresh dispatch (local only)
     int64_t slot_scratch_offset; // i32[slot_scratch_ints] expert-major slot -> row*K+k of a fresh dispatch (local only)
     int64_t slot_scratch_ints;
     int64_t num_bytes;
 
     // ctrl sub-layout, in int32 units from ctrl_offset.
-    static constexpr int kTicketStage = 0, kTicketPush = 1, kGoWord = 2, kCtrlHeaderInts = 16;  // words 4..6: status
+    static constexpr int kTicketStage = 0, kTicketCombine = 1, kGoWord = 2, kTicketCopy = 3, kCtrlHeaderInts = 16;  // words 4..6: status
     NEP_HD int64_t ctrl_count_acc() const { return kCtrlHeaderInts; }                         // i32[R + E]
     NEP_HD int64_t ctrl_row_cursor() const { return ctrl_count_acc() + ranks + num_experts; }  // i32[R]
     NEP_HD int64_t ctrl_expert_cursor() const { return ctrl_row_cursor() + ranks; }            // i32[L]
@@ -69,7 +73,7 @@ struct WindowLayout {
     NEP_HD int64_t row_bytes() const { return wire_row_bytes(hidden, topk); }
     NEP_HD int64_t msg_ints() const { return count_msg_ints(local_experts); }
 
-    static WindowLayout make(int ranks, int64_t max_tokens, int hidden, int topk, int64_t num_experts) {
+    static WindowLayout make(int ranks, int64_t max_tokens, int hidden, int topk, int64_t num_experts, bool per_rank_reduction = false) {
         if (ranks <= 0 || ranks > kMaxRanks || (ranks & (ranks - 1)) != 0)
             throw std::invalid_argument("world size must be a power of two in [1,32]");
         if (max_tokens <= 0 || hidden <= 0 || topk <= 0 || topk > kMaxTopk)
@@ -100,10 +104,13 @@ struct WindowLayout {
         w.routing_in_offset = take(2 * w.routing_in_stride);
         w.stage_rows_stride = align_up(max_tokens * w.row_bytes(), kRegionAlign);
         w.stage_rows_offset = take(2 * w.stage_rows_stride);
-        w.ret_w_stride = align_up(max_tokens * topk * 4, kRegionAlign);
-        w.ret_w_offset = take(2 * w.ret_w_stride);
-        w.ret_stride = align_up(int64_t(topk) * max_tokens * hidden * 2, kRegionAlign);
-        w.ret_offset = take(2 * w.ret_stride);
+        // One row per (token, expert rank) comes back when the buffer pre-reduces per rank: min(R, K) partitions
+        // are enough, indexed by the expert rank when every rank has its own.
+        w.ret_parts = per_rank_reduction ? (ranks < topk ? ranks : topk) : topk;
+        w.rank_indexed = (per_rank_reduction && ranks <= topk) ? 1 : 0;
+        w.ret_w_offset = take(max_tokens * topk * 4);
+        w.ret_flag_offset = take(int64_t(w.ret_parts) * max_tokens * 4);
+        w.ret_offset = take(int64_t(w.ret_parts) * max_tokens * hidden * 2);
         w.meta_scratch_offset = take(int64_t(ranks) * max_tokens * (topk + 2) * 4);
         w.slot_scratch_ints = int64_t(ranks) * max_tokens * topk + int64_t(w.local_experts) * 128;
         w.slot_scratch_offset = take(w.slot_scratch_ints * 4);

@@ -46,7 +46,17 @@ public:
     uint64_t reserve_epochs(int count);
     uint64_t last_epoch() const { return epoch_; }
     int next_dispatch_parity() { return int(dispatch_seq_++ & 1); }
-    int next_combine_parity() { return int(combine_seq_++ & 1); }
+    // A combine reserves one epoch, which it signals to every peer when its pushes and its reduction are done,
+    // and learns the epoch of the previous combine: before writing into a peer's (single) return area it waits
+    // until that peer has signalled at least that epoch, i.e. has finished reading the previous contents.
+    struct CombineEpochs {
+        uint64_t epoch, wait_epoch;  // wait_epoch 0: no earlier combine
+    };
+    CombineEpochs begin_combine() {
+        const uint64_t previous = last_combine_epoch_;
+        last_combine_epoch_ = reserve_epochs(1);
+        return CombineEpochs{last_combine_epoch_, previous};
+    }
 
     CommonParams common() const;
     void set_wait_timeout(double seconds) { timeout_ns_ = uint64_t(seconds * 1e9); }
@@ -83,7 +93,7 @@ private:
     void* peers_[kMaxRanks] = {};
     bool imported_[kMaxRanks] = {};
     bool connected_ = false, closed_ = false, unmapped_ = false, failed_ = false;
-    uint64_t epoch_ = 0, dispatch_seq_ = 0, combine_seq_ = 0;
+    uint64_t epoch_ = 0, dispatch_seq_ = 0, last_combine_epoch_ = 0;
     uint64_t timeout_ns_;
     volatile int64_t* mailbox_ = nullptr;       // host pointer
     volatile int64_t* mailbox_dev_ = nullptr;   // device alias

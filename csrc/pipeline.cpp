@@ -27,7 +27,6 @@ namespace {
 
 constexpr int kFusedDispatchDefaultTokens = 64;
 constexpr int kFusedDefaultBlocks = 1024;  // i.e. bounded by the SM budget and co-residency only
-constexpr int kFusedCombineDefaultTokens = 512;
 
 void cuda_check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
@@ -57,21 +56,19 @@ struct PhaseMarks {
 };
 PhaseMarks g_marks;
 
-// Single-launch paths for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
-// stage, peer barrier and pull as one cooperative launch; combines whose ranks contributed at most
-// `combine_tokens` source tokens run push, peer barrier and reduce as one.  `blocks` bounds their grids
-// (every block must be resident at once and spins on one word while the last block runs the peer
-// barrier).  Defaults come from NANOEP_FUSED_DISPATCH_TOKENS / NANOEP_FUSED_COMBINE_TOKENS /
-// NANOEP_FUSED_BLOCKS (0 tokens switches a path off) and can be changed at run time.
+// Single-launch path for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
+// stage, peer barrier and pull as one cooperative launch; `blocks` bounds its grid (every block must be
+// resident at once and spins on one word while the last block runs the peer barrier).  Defaults come from
+// NANOEP_FUSED_DISPATCH_TOKENS / NANOEP_FUSED_BLOCKS (0 tokens switches the path off) and can be changed
+// at run time.  (A combine is one launch at every size.)
 struct FusedLimitsState {
-    std::atomic<int64_t> dispatch_tokens, combine_tokens, blocks;
+    std::atomic<int64_t> dispatch_tokens, blocks;
     FusedLimitsState() {
         auto read = [](const char* name, int64_t fallback) {
             const char* env = std::getenv(name);
             return env != nullptr ? std::atoll(env) : fallback;
         };
         dispatch_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_DISPATCH_TOKENS", kFusedDispatchDefaultTokens));
-        combine_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_COMBINE_TOKENS", kFusedCombineDefaultTokens));
         blocks = std::max<int64_t>(1, read("NANOEP_FUSED_BLOCKS", kFusedDefaultBlocks));
     }
 };
@@ -80,7 +77,6 @@ FusedLimitsState& fused_state() {
     return state;
 }
 int64_t fused_dispatch_max_tokens() { return fused_state().dispatch_tokens.load(std::memory_order_relaxed); }
-int64_t fused_combine_max_tokens() { return fused_state().combine_tokens.load(std::memory_order_relaxed); }
 int64_t fused_max_blocks() { return fused_state().blocks.load(std::memory_order_relaxed); }
 
 struct DeviceLimits {
@@ -534,73 +530,60 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
         out.event = finish(s, async_op, std::move(inputs), std::move(results));
         return out;
     }
-    std::vector<PushParams> push(n);
-    std::vector<ReduceParams> reduce(n);
+    std::vector<CombineParams> params(n);
     std::vector<at::Tensor> keep;
+    TORCH_CHECK(ring.stages >= 2 && ring.warps < kCombineThreads / 32, "combine ring plan out of range");
     {
         c10::cuda::CUDAStreamGuard pool(consumer);
         for (int i = 0; i < n; ++i) {
             const auto& m = meta[i];
             const int64_t T = m[5].size(0);
-            const int parity = wins[i]->next_combine_parity();
-            PushParams& p = push[i];
-            p.c = wins[i]->common();
-            p.y = reinterpret_cast<const __nv_bfloat16*>(xs[i].data_ptr());
-            p.w = weighted ? weights[i]->data_ptr<float>() : nullptr;
-            p.meta = m[0].data_ptr<int>();
-            p.slot_map = expand ? m[7].data_ptr<int>() : nullptr;
-            p.recv_rank_prefix = m[6].data_ptr<int64_t>();
-            p.rows = int(m[0].size(0));
-            p.capacity = int(capacity[i]);
-            p.mode = !expand ? kPushCompact : allow_multiple_reduction ? kPushExpandedReduce : kPushExpanded;
-            p.parity = parity;
-            p.stages = ring.stages;
-            p.epoch = wins[i]->reserve_epochs(1);
+            const PeerWindow::CombineEpochs epochs = wins[i]->begin_combine();
             auto& o = out.outputs[i];
             o.resize(2);
             o[0] = at::empty({T, L.hidden}, bf16);
             o[1] = weighted ? at::empty({T, L.topk}, f32) : at::empty({0}, f32);
-            ReduceParams& r = reduce[i];
-            r.c = p.c;
-            r.topk = m[5].data_ptr<int64_t>();
-            r.bias = bias[i].has_value() ? reinterpret_cast<const __nv_bfloat16*>(bias[i]->data_ptr()) : nullptr;
-            r.out = reinterpret_cast<__nv_bfloat16*>(o[0].data_ptr());
-            r.w_out = weighted ? o[1].data_ptr<float>() : nullptr;
-            r.tokens = int(T);
-            r.parity = parity;
-            r.sum_all_choices = (expand && !allow_multiple_reduction) ? 1 : 0;
+            CombineParams& p = params[i];
+            p.c = wins[i]->common();
+            p.y = reinterpret_cast<const __nv_bfloat16*>(xs[i].data_ptr());
+            p.w = weighted ? weights[i]->data_ptr<float>() : nullptr;
+            p.meta = m[0].data_ptr<int>();
+            p.recv_rank_prefix = m[6].data_ptr<int64_t>();
+            p.rows = int(m[0].size(0));
+            p.capacity = int(capacity[i]);
+            p.mode = !expand ? kPushCompact : allow_multiple_reduction ? kPushExpandedReduce : kPushExpanded;
+            p.stages = ring.stages;
+            p.push_warps = ring.warps;
+            p.topk = m[5].data_ptr<int64_t>();
+            p.bias = bias[i].has_value() ? reinterpret_cast<const __nv_bfloat16*>(bias[i]->data_ptr()) : nullptr;
+            p.out = reinterpret_cast<__nv_bfloat16*>(o[0].data_ptr());
+            p.w_out = weighted ? o[1].data_ptr<float>() : nullptr;
+            p.tokens = int(T);
+            p.sum_all_choices = (expand && !allow_multiple_reduction) ? 1 : 0;
+            p.epoch = epochs.epoch;
+            p.wait_epoch = epochs.wait_epoch;
+            TORCH_CHECK(p.sum_all_choices == 0 || L.ret_parts == L.topk, "this buffer's return area holds one partition per rank only");
         }
     }
     {
         c10::cuda::CUDAStreamGuard on_comm(s.work);
-        int64_t max_items = 1, max_tokens_now = 1;
+        int64_t max_transfers = 1, max_tokens_now = 1;
         for (int i = 0; i < n; ++i) {
-            max_items = std::max<int64_t>(max_items, expand ? capacity[i] : meta[i][0].size(0) * L.ranks);
+            max_transfers = std::max<int64_t>(max_transfers, expand && !allow_multiple_reduction ? capacity[i] : meta[i][0].size(0));
             max_tokens_now = std::max<int64_t>(max_tokens_now, meta[i][5].size(0));
         }
-        // Small combines: push, peer barrier and reduce go out as ONE cooperative launch.
-        const bool fuse_small = max_tokens_now <= fused_combine_max_tokens();
-        for (int i = 0; i < n; ++i) push[i].fused = fuse_small ? 1 : 0;
-        const PushParams* pdev = upload(push, keep, cs);
-        const ReduceParams* rdev = upload(reduce, keep, cs);
+        const int reduce_warps = kCombineThreads / 32 - ring.warps;
+        // Every block holds transfer warps and reduce warps: enough blocks for the larger of the two jobs.
+        const int64_t wanted = std::max<int64_t>((max_transfers + ring.warps - 1) / ring.warps, (max_tokens_now + reduce_warps - 1) / reduce_warps);
+        // A whole logical group in one launch waits on itself: all its blocks must be resident (cooperative launch).
+        const bool group_launch = n > 1;
+        const int64_t cap = group_launch ? std::min<int64_t>(num_sms, lim.sms / n) : num_sms;
+        const int grid = int(std::max<int64_t>(1, std::min<int64_t>(cap, wanted)));
+        const CombineParams* dev = upload(params, keep, cs);
         g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
-        if (fuse_small) {
-            // every block must be resident at once (one block per SM with this ring): bound the grid
-            const int64_t work = std::max<int64_t>(max_items, max_tokens_now);
-            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), fused_max_blocks(),
-                                                                               (work + ring.warps - 1) / ring.warps})));
-            cuda_check(launch_fused_combine(pdev, rdev, LaunchShape{fused_grid, n}, ring.warps, ring.smem_bytes, cs), "fused combine launch");
-            g_marks.mark("fused_combine", cs);
-        } else {
-            const int push_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
-            cuda_check(launch_push(pdev, LaunchShape{push_grid, n}, ring.warps, ring.smem_bytes, cs), "push launch");
-            g_marks.mark("push", cs);
-            PeerWindow::launches += 1;
-            const int reduce_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * lim.sms, (max_tokens_now + 15) / 16)));
-            cuda_check(launch_reduce(rdev, LaunchShape{reduce_grid, n}, cs), "reduce launch");
-            g_marks.mark("reduce", cs);
-        }
+        cuda_check(launch_combine(dev, LaunchShape{grid, n}, ring.smem_bytes, cs, group_launch), "combine launch");
+        g_marks.mark("combine", cs);
     }
     std::vector<at::Tensor> inputs, results;
     for (int i = 0; i < n; ++i) {
@@ -615,12 +598,12 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
 }
 
 std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, const std::vector<std::vector<at::Tensor>>& meta,
-                                       const std::vector<int64_t>& parity, const std::vector<c10::optional<at::Tensor>>& bias) {
+                                       const std::vector<c10::optional<at::Tensor>>& bias) {
     // Second half of a combine whose push was done by another kernel (the scatter epilogue of the
     // down-projection GEMM): peer barrier, then the source-side reduction, on the current stream.
     validate_group(wins);
     const int n = int(wins.size());
-    TORCH_CHECK(int(meta.size()) == n && int(parity.size()) == n && int(bias.size()) == n, "per-rank argument lists must have one entry per rank");
+    TORCH_CHECK(int(meta.size()) == n && int(bias.size()) == n, "per-rank argument lists must have one entry per rank");
     const WindowLayout& L = wins[0]->layout();
     const int device = wins[0]->device();
     c10::cuda::CUDAGuard device_guard(device);
@@ -635,7 +618,8 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
         const int64_t T = meta[i][5].size(0);
         wins[i]->check_status();
         barrier[i].c = wins[i]->common();
-        barrier[i].epoch = wins[i]->reserve_epochs(1);
+        barrier[i].epoch = wins[i]->begin_combine().epoch;  // a later combine waits for this barrier's epoch before it writes
+        TORCH_CHECK(L.ret_parts == L.topk, "this buffer's return area holds one partition per rank only");
         outs[i] = at::empty({T, L.hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device));
         ReduceParams& r = reduce[i];
         r.c = barrier[i].c;
@@ -649,7 +633,6 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
         }
         r.out = reinterpret_cast<__nv_bfloat16*>(outs[i].data_ptr());
         r.tokens = int(T);
-        r.parity = int(parity[i]);
         r.sum_all_choices = 1;
     }
     const BarrierParams* bdev = upload(barrier, keep, cs);
@@ -661,11 +644,10 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
     return outs;
 }
 
-FusedLimits fused_limits() { return FusedLimits{fused_dispatch_max_tokens(), fused_combine_max_tokens(), fused_max_blocks()}; }
+FusedLimits fused_limits() { return FusedLimits{fused_dispatch_max_tokens(), fused_max_blocks()}; }
 
-void set_fused_limits(int64_t dispatch_tokens, int64_t combine_tokens, int64_t blocks) {
+void set_fused_limits(int64_t dispatch_tokens, int64_t blocks) {
     if (dispatch_tokens >= 0) fused_state().dispatch_tokens = dispatch_tokens;
-    if (combine_tokens >= 0) fused_state().combine_tokens = combine_tokens;
     if (blocks >= 1) fused_state().blocks = blocks;
 }
 

@@ -53,16 +53,16 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
                    int64_t comm_stream, int64_t previous_event, bool async_op);
 
 std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, const std::vector<std::vector<at::Tensor>>& meta,
-                                       const std::vector<int64_t>& parity, const std::vector<c10::optional<at::Tensor>>& bias);
+                                       const std::vector<c10::optional<at::Tensor>>& bias);
 
 // Per-phase device times (name, microseconds) of the operations issued since the last call.
-// Token thresholds and grid bound of the single-launch paths for small calls (see pipeline.cpp).
+// Token threshold and grid bound of the single-launch cached dispatch for small calls (see pipeline.cpp).
 struct FusedLimits {
-    int64_t dispatch_tokens, combine_tokens, blocks;
+    int64_t dispatch_tokens, blocks;
 };
 FusedLimits fused_limits();
 // Negative token values / blocks < 1 leave the respective setting unchanged.
-void set_fused_limits(int64_t dispatch_tokens, int64_t combine_tokens, int64_t blocks);
+void set_fused_limits(int64_t dispatch_tokens, int64_t blocks);
 
 void set_phase_timing(bool enabled);
 std::vector<std::pair<std::string, double>> take_phase_timings();

@@ -37,6 +37,14 @@ __device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ int ld_relaxed_sys(const int* p) {
     int v;
     asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -96,6 +104,37 @@ __device__ __forceinline__ bool peer_barrier_warp(
         fence_acq_rel_sys();
         auto* remote = reinterpret_cast<uint64_t*>(static_cast<char*>(peers[lane]) + signal_offset) + rank;
         st_release_sys(remote, epoch);
+        const auto* local = reinterpret_cast<const uint64_t*>(static_cast<const char*>(peers[rank]) + signal_offset) + lane;
+        const uint64_t start = global_timer_ns();
+        uint32_t spins = 0;
+        while (ld_acquire_sys(local) < epoch) {
+            __nanosleep(32);
+            if ((++spins & 63u) == 0u && global_timer_ns() - start > timeout_ns) {
+                report(status, kBarrierTimeout, uint32_t(lane), tag);
+                ok = false;
+                break;
+            }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    fence_acq_rel_sys();
+    return ok;
+}
+
+// The two halves of the barrier on their own.  `peer_signal_warp`: lane p < ranks publishes `epoch` to peer p
+// and returns at once.  `peer_wait_warp`: wait until every peer's value in the local slots reaches `epoch`.
+__device__ __forceinline__ void peer_signal_warp(void* const* peers, int rank, int ranks, int64_t signal_offset, uint64_t epoch) {
+    const int lane = threadIdx.x & 31;
+    if (lane < ranks) {
+        fence_acq_rel_sys();
+        st_release_sys(reinterpret_cast<uint64_t*>(static_cast<char*>(peers[lane]) + signal_offset) + rank, epoch);
+    }
+}
+__device__ __forceinline__ bool peer_wait_warp(
+    void* const* peers, int rank, int ranks, int64_t signal_offset, uint64_t epoch, uint64_t timeout_ns, const StatusRef& status, uint32_t tag) {
+    const int lane = threadIdx.x & 31;
+    bool ok = true;
+    if (lane < ranks) {
         const auto* local = reinterpret_cast<const uint64_t*>(static_cast<const char*>(peers[rank]) + signal_offset) + lane;
         const uint64_t start = global_timer_ns();
         uint32_t spins = 0;

@@ -44,7 +44,8 @@ class ExpertParallelMoE:
             raise ValueError("hidden must be a multiple of 256 and I a multiple of 64")
         self.buffer, self.w13, self.w2 = buffer, w13, w2
         self.inner = inner
-        self.fuse_combine = fuse_combine
+        # The scatter epilogue returns one row per choice; a buffer that pre-reduces per rank has no partitions for that.
+        self.fuse_combine = fuse_combine and not buffer.allow_multiple_reduction
         self.overlap_dispatch = overlap_dispatch
         self.device = w13.device
         self.comm_ring_bytes = int(comm_ring_bytes)
@@ -104,11 +105,10 @@ class ExpertParallelMoE:
         self.last_handle = got.handle
         if self.fuse_combine:
             window = buf.window
-            parity = self._ext.next_combine_parity(window)
-            self._ext.grouped_gemm_scatter(window, parity, h, self.w2, offsets, got.handle.slot_map, got.handle.layout.recv_metadata,
+            self._ext.grouped_gemm_scatter(window, h, self.w2, offsets, got.handle.slot_map, got.handle.layout.recv_metadata,
                                            got.topk_weights, gg.status_tensor(self.device), 0, 5.0, pairs)
             mark("down_gemm_scatter")
-            out = self._ext.combine_finish([window], [handle_metadata(got.handle)], [parity], [bias])[0]
+            out = self._ext.combine_finish([window], [handle_metadata(got.handle)], [bias])[0]
             mark("barrier+reduce")
             self._collect(marks)
             return out

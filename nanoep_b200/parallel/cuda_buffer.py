@@ -142,6 +142,7 @@ class CudaBuffer:
                 config.num_topk,
                 config.num_experts,
                 float(wait_timeout_s),
+                bool(allow_multiple_reduction),
             )
             self._layout = self._window.layout()
             return self._window.export_handle()
@@ -193,6 +194,10 @@ class CudaBuffer:
     @property
     def world_size(self) -> int:
         return self._world_size
+
+    @property
+    def allow_multiple_reduction(self) -> bool:
+        return self._allow_multiple_reduction
 
     @property
     def comm_stream(self):

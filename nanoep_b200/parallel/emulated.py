@@ -41,7 +41,8 @@ class EmulatedGroup:
         with torch.cuda.device(self.device):
             self.windows = [
                 self._backend.PeerWindow(
-                    r, world_size, config.num_max_tokens_per_rank, config.hidden, config.num_topk, config.num_experts, float(wait_timeout_s)
+                    r, world_size, config.num_max_tokens_per_rank, config.hidden, config.num_topk, config.num_experts, float(wait_timeout_s),
+                    bool(allow_multiple_reduction),
                 )
                 for r in range(world_size)
             ]

@@ -22,7 +22,7 @@ def count_message_ints(local_experts: int) -> int:
     return 2 + local_experts
 
 
-def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_experts: int) -> dict:
+def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_experts: int, per_rank_reduction: bool = False) -> dict:
     local = num_experts // ranks
     region = 256
     at = 0
@@ -43,10 +43,13 @@ def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_expe
     out["routing_in_offset"] = take(2 * out["routing_in_stride"])
     out["stage_rows_stride"] = align(max_tokens * wire_row_bytes(hidden, topk), region)
     out["stage_rows_offset"] = take(2 * out["stage_rows_stride"])
-    out["ret_w_stride"] = align(max_tokens * topk * 4, region)
-    out["ret_w_offset"] = take(2 * out["ret_w_stride"])
-    out["ret_stride"] = align(topk * max_tokens * hidden * 2, region)
-    out["ret_offset"] = take(2 * out["ret_stride"])
+    # return area: one copy; P partitions of [Tmax, H] bf16, a u32 arrival flag per (partition, token), fp32 weights [Tmax, K]
+    parts = min(ranks, topk) if per_rank_reduction else topk
+    out["ret_parts"] = parts
+    out["rank_indexed"] = int(per_rank_reduction and ranks <= topk)
+    out["ret_w_offset"] = take(max_tokens * topk * 4)
+    out["ret_flag_offset"] = take(parts * max_tokens * 4)
+    out["ret_offset"] = take(parts * max_tokens * hidden * 2)
     out["meta_scratch_offset"] = take(ranks * max_tokens * (topk + 2) * 4)
     out["slot_scratch_offset"] = take((ranks * max_tokens * topk + local * 128) * 4)
     out["num_bytes"] = at
