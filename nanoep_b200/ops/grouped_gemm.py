@@ -34,7 +34,7 @@ def check_status(device=None):
     code, cta = (int(v) for v in st[:2].tolist())
     if code != 0:
         st.zero_()
-        reasons = {101: "an operand pipeline wait timed out", 102: "a row block's ready counter never filled",
+        reasons = {101: "an operand pipeline wait timed out", 102: "the wait for a row block's ready counter timed out",
                    103: "expert_offsets are not multiples of 128 from 0 to the row count", 104: "handle metadata names an impossible rank, token or row"}
         raise RuntimeError(f"nanoep_b200 grouped GEMM status {code} ({reasons.get(code, 'unknown')}), detail {cta}")
 

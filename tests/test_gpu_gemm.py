@@ -113,3 +113,16 @@ def test_cta_pair_kernel_matches_reference_and_single_cta(swiglu):
     torch.cuda.synchronize()
     gg.check_status()
     assert torch.equal(small, single)
+
+
+def test_offsets_off_the_block_grid_are_reported():
+    """One expert per 128-row block: offsets that are not multiples of 128, or that do not end at the row count, are refused."""
+    a = torch.zeros(256, 128, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(2, 256, 128, dtype=torch.bfloat16, device="cuda")
+    for bad in ([0, 100, 256], [0, 128, 128]):
+        out = gg.grouped_gemm(a, w, torch.tensor(bad, dtype=torch.int64, device="cuda"))
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="expert_offsets"):
+            gg.check_status()
+        del out
+    assert torch.ones(2, device="cuda").sum().item() == 2
