@@ -26,6 +26,8 @@ py::dict layout_dict(const nep::WindowLayout& w) {
     d["counts_in_stride"] = w.counts_in_stride;
     d["routing_in_offset"] = w.routing_in_offset;
     d["routing_in_stride"] = w.routing_in_stride;
+    d["chunks_in_offset"] = w.chunks_in_offset;
+    d["chunks_in_stride"] = w.chunks_in_stride;
     d["stage_rows_offset"] = w.stage_rows_offset;
     d["stage_rows_stride"] = w.stage_rows_stride;
     d["ret_parts"] = w.ret_parts;
@@ -73,11 +75,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("layout", [](const PeerWindow& w) { return layout_dict(w.layout()); })
         .def("export_handle", [](PeerWindow& w) { return py::bytes(w.export_handle()); })
         .def("import_handles",
-             [](PeerWindow& w, const std::vector<py::bytes>& handles) {
+             [](PeerWindow& w, const std::vector<py::bytes>& handles, const std::vector<int>& peer_devices) {
                  std::vector<std::string> raw;
                  for (const auto& h : handles) raw.emplace_back(std::string(h));
-                 w.import_handles(raw);
-             })
+                 w.import_handles(raw, peer_devices);
+             },
+             py::arg("handles"), py::arg("peer_devices") = std::vector<int>{})
         .def("adopt_peers", &PeerWindow::adopt_peers)
         .def("close_peer_mappings", &PeerWindow::close_peer_mappings)
         .def("close", &PeerWindow::close)
@@ -170,6 +173,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     });
     m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1);
     m.def("set_phase_timing", &nep::set_phase_timing);
+    m.def("set_combine_trace", &nep::set_combine_trace, py::arg("enabled"), py::arg("store_depth") = 0, py::arg("reduce_group") = 0);
+    m.def("take_combine_trace", &nep::take_combine_trace);
     m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });
     m.def("format_status", &nep::format_status);

@@ -143,7 +143,13 @@ __device__ bool stage_body(const StageParams& p) {
                 if (lane == __ffs(same) - 1) atomicAdd(&s_counts[d], 1);
             }
             const unsigned dmask = __reduce_or_sync(kFull, valid ? (1u << d) : 0u);
-            if (lane < R) p.dst_slots[int64_t(t) * R + lane] = ((dmask >> lane) & 1u) ? int64_t(t) : int64_t(-1);
+            if (lane < R) {
+                const bool goes = (dmask >> lane) & 1u;
+                p.dst_slots[int64_t(t) * R + lane] = goes ? int64_t(t) : int64_t(-1);
+                // rows this rank sends to destination `lane` out of the token's chunk of 32: the receivers turn these
+                // into row offsets, so that receive rows are ordered by (source rank, source token)
+                if (goes) atomicAdd(ctrl + L.ctrl_chunk_acc() + int64_t(lane) * L.chunks_per_rank() + (t >> 5), 1);
+            }
         }
     }
 
@@ -168,6 +174,15 @@ __device__ bool stage_body(const StageParams& p) {
             st_relaxed_sys(remote, v);
         }
         for (int d = tid; d < R; d += blockDim.x) p.send_counts[d] = __ldcg(count_acc + d);
+        // per-chunk row counts go to their destination (the accumulators are cleared for the next dispatch)
+        const int cps = int(L.chunks_per_rank()), my_chunks = (p.tokens + 31) / 32;
+        int* chunk_acc = ctrl + L.ctrl_chunk_acc();
+        for (int i = tid; i < R * my_chunks; i += blockDim.x) {
+            const int d = i / my_chunks, c = i % my_chunks;
+            int* remote = reinterpret_cast<int*>(window(p.c, d) + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride) + p.c.rank * cps + c;
+            st_relaxed_sys(remote, __ldcg(chunk_acc + d * cps + c));
+            chunk_acc[d * cps + c] = 0;
+        }
         __syncthreads();
         for (int i = tid; i < R + E; i += blockDim.x) count_acc[i] = 0;
     }
@@ -241,6 +256,24 @@ __device__ bool stage_body(const StageParams& p) {
             s_total[1] = carry;
         }
     }
+    // Every source's per-chunk row counts become exclusive prefixes: chunk c of source s starts at receive row
+    // recv_prefix[s] + chunk_prefix[s][c].  The total must equal the source's announced row count.
+    {
+        const int cps = int(L.chunks_per_rank());
+        int* chunks = reinterpret_cast<int*>(win + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride);
+        for (int s = warp; s < R; s += wpb) {
+            const int n_chunks = (ld_relaxed_sys(in + s * msg + 1) + 31) / 32;
+            int carry = 0;
+            for (int base = 0; base < n_chunks; base += 32) {
+                const int c = base + lane;
+                const int v = c < n_chunks ? ld_relaxed_sys(chunks + s * cps + c) : 0;
+                const int incl = warp_inclusive_sum(v);
+                if (c < n_chunks) chunks[s * cps + c] = carry + incl - v;
+                carry += __shfl_sync(kFull, incl, 31);
+            }
+            if (lane == 0 && carry != ld_relaxed_sys(in + s * msg)) report(status, kSlotOverflow, uint32_t(s), kTagStage);
+        }
+    }
     __syncthreads();
     if (tid == 0) {
         __threadfence_system();
@@ -266,8 +299,8 @@ __device__ void plan_body(const PlanParams& p) {
     const int* prefix = ctrl + L.ctrl_recv_prefix();
     const int* src_tokens = ctrl + L.ctrl_src_tokens();
     const int* eoff = ctrl + L.ctrl_expert_offsets();
-    int* row_cursor = ctrl + L.ctrl_row_cursor();
     int* expert_cursor = ctrl + L.ctrl_expert_cursor();
+    const int* chunk_prefix = reinterpret_cast<const int*>(window(p.c, p.c.rank) + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride);
     int* meta = reinterpret_cast<int*>(window(p.c, p.c.rank) + L.meta_scratch_offset);
     int* mine = s_chunk + warp * 32 * K;
     const StatusRef status = status_of(p.c);
@@ -313,9 +346,8 @@ __device__ void plan_body(const PlanParams& p) {
             }
         const unsigned hm = __ballot_sync(kFull, has);
         if (hm == 0) continue;
-        int base_row = 0;
-        if (lane == 0) base_row = atomicAdd(&row_cursor[s], __popc(hm));
-        base_row = __shfl_sync(kFull, base_row, 0);
+        // rows of a source are ordered by token: the chunk's first row comes from the prefix the stage kernel built
+        const int base_row = chunk_prefix[s * cps + (tok0 >> 5)];
         if (has) {
             const int row = prefix[s] + base_row + __popc(hm & lanemask_lt());
             if (row >= prefix[s + 1]) {
@@ -628,40 +660,100 @@ __device__ __forceinline__ int4 pack8(const float* acc) {
     return v;
 }
 
-// Arrival flags of the two newest stores of a transfer warp.  A flag is published only after the bulk group
-// that carried its row has COMPLETED (cp.async.bulk.wait_group, not .read): two groups may stay in flight.
-struct FlagQueue {
-    uint32_t* older;
-    uint32_t* newer;
-    uint32_t tag;
-    __device__ __forceinline__ void publish(uint32_t* flag) const {
-        if ((threadIdx.x & 31) == 0 && flag != nullptr) {
-            fence_proxy_async();
-            st_release_sys_u32(flag, tag);
-        }
+// Arrival flags are published by a dedicated warp, not by the transfer warps: a flag needs a system-scope
+// release after its row has landed, and that fence waits for remote stores in flight.  A transfer warp only
+// appends the flag's address to its ring on this board and reports how many of its bulk stores have COMPLETED
+// (cp.async.bulk.wait_group, not .read; up to kStoresInFlight may be pending).  The publisher warp sweeps the
+// boards, fences once per sweep and writes the flags of everything that completed since its last sweep.
+constexpr int kFlagRing = 32;  // entries per transfer warp
+constexpr int kMaxPushWarps = 8;
+__device__ __forceinline__ void bulk_wait_depth(int depth) {
+    switch (depth) {
+        case 2: bulk_wait<2>(); break;
+        case 6: bulk_wait<6>(); break;
+        case 8: bulk_wait<8>(); break;
+        case 12: bulk_wait<12>(); break;
+        default: bulk_wait<4>(); break;
     }
+}
+struct FlagBoard {
+    uint32_t* ring[kMaxPushWarps][kFlagRing];
+    int completed[kMaxPushWarps];  // transfers whose rows have landed (written by the transfer warp, release)
+    int published[kMaxPushWarps];  // transfers whose flags are out (written by the publisher)
+    int finished[kMaxPushWarps];   // the transfer warp has no more work
+};
+
+struct FlagWriter {  // a transfer warp's end of the board (all lanes hold the same values)
+    FlagBoard* board;
+    int warp;
+    int produced;
+    int depth;  // bulk stores that may be pending before the warp waits
+    uint64_t timeout_ns;
     // Call right after committing the bulk group of the row that `flag` announces.
     __device__ __forceinline__ void push(uint32_t* flag) {
-        bulk_wait_read<1>();  // the ring stage of the previous row may be refilled
-        bulk_wait<2>();       // the row before that has landed
-        __syncwarp();         // other lanes' gate-weight stores for that row are ordered before the flag
-        publish(older);
-        older = newer;
-        newer = flag;
+        const int lane = threadIdx.x & 31;
+        if (lane == 0) {
+            volatile int* published = board->published + warp;
+            if (produced - *published >= kFlagRing) {  // ring full: the publisher is behind (bounded wait)
+                const uint64_t start = global_timer_ns();
+                while (produced - *published >= kFlagRing && global_timer_ns() - start < timeout_ns) __nanosleep(64);
+            }
+            board->ring[warp][produced % kFlagRing] = flag;
+        }
+        ++produced;
+        bulk_wait_read<1>();              // the ring stage of the previous row may be refilled
+        bulk_wait_depth(depth);           // everything older than the newest `depth` rows has landed
+        __syncwarp();                     // other lanes' gate-weight stores are ordered before the hand-over below
+        if (lane == 0 && produced > depth) st_release_cta_smem(board->completed + warp, produced - depth);
     }
-    __device__ __forceinline__ void drain() {
+    __device__ __forceinline__ void finish() {
         bulk_wait<0>();
         __syncwarp();
-        publish(older);
-        publish(newer);
-        older = newer = nullptr;
+        if ((threadIdx.x & 31) == 0) {
+            st_release_cta_smem(board->completed + warp, produced);
+            st_release_cta_smem(board->finished + warp, 1);
+        }
     }
 };
+
+// The publisher warp of a combine CTA.
+__device__ void combine_publish_role(const CombineParams& p, FlagBoard* board) {
+    const int lane = threadIdx.x & 31, PW = p.push_warps;
+    const uint32_t tag = combine_tag(p.epoch);
+    int pub = 0;  // lane w < PW: flags of transfer warp w published so far
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+        const int fin = lane < PW ? ld_acquire_cta_smem(board->finished + lane) : 1;
+        const int done = lane < PW ? ld_acquire_cta_smem(board->completed + lane) : 0;
+        const unsigned fresh = __ballot_sync(kFull, lane < PW && done > pub);
+        if (fresh != 0) {
+            fence_acq_rel_sys();  // one release for everything that landed since the last sweep
+            for (unsigned left = fresh; left != 0; left &= left - 1) {
+                const int w = __ffs(left) - 1;
+                const int from = __shfl_sync(kFull, pub, w), to = __shfl_sync(kFull, done, w);
+                for (int i = from + lane; i < to; i += 32) st_relaxed_sys_u32(board->ring[w][i % kFlagRing], tag);
+            }
+            __syncwarp();  // every ring entry has been read before its slot is handed back
+            if (lane < PW && done > pub) {
+                pub = done;
+                *(volatile int*)(board->published + lane) = pub;
+            }
+        }
+        if (__all_sync(kFull, fin != 0 && pub == done)) break;
+        if (fresh == 0) {
+            __nanosleep(200);
+            if (global_timer_ns() - start > 4 * p.c.timeout_ns) {  // transfer warps give up long before this
+                if (lane == 0) report(status_of(p.c), kCopyTimeout, 0xfffeu, kTagPush);
+                break;
+            }
+        }
+    }
+}
 
 // Transfer warps.  Receive rows are visited round-robin over the source ranks (SourceWalk), so at every moment
 // the warps of a GPU address all destinations evenly; a row of the expert-major layout yields one transfer per
 // local slot.
-__device__ void combine_push_role(const CombineParams& p, char* smem) {
+__device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard* board) {
     const WindowLayout& L = p.c.layout;
     const int R = L.ranks, K = L.topk, H = L.hidden;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, PW = p.push_warps;
@@ -673,7 +765,8 @@ __device__ void combine_push_role(const CombineParams& p, char* smem) {
     const int S = p.stages;
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
     const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
-    FlagQueue flags{nullptr, nullptr, combine_tag(p.epoch)};
+    const int depth = (p.store_depth == 2 || p.store_depth == 6 || p.store_depth == 8 || p.store_depth == 12) ? p.store_depth : 4;
+    FlagWriter flags{board, warp, 0, depth, p.c.timeout_ns};
 
     if (p.mode == kPushExpandedReduce) {
         // FP32 sum of the row's local slots, one bf16 round, one store per (token, this rank).
@@ -738,7 +831,7 @@ __device__ void combine_push_role(const CombineParams& p, char* smem) {
             bulk_commit();
             flags.push(ret_flag(p.c, src, part, tok));
         }
-        flags.drain();
+        flags.finish();
         return;
     }
 
@@ -803,7 +896,7 @@ __device__ void combine_push_role(const CombineParams& p, char* smem) {
         flags.push(ret_flag(p.c, now.src, part, now.tok));
         if (more && (more = next(ahead))) issue(ahead, issued++);
     }
-    flags.drain();
+    flags.finish();
 }
 
 // Which return partitions hold a row for source token `t`, as a mask over the lanes (choices) that name them;
@@ -825,104 +918,128 @@ __device__ __forceinline__ unsigned expected_parts(const int64_t* topk, int t, i
     return __ballot_sync(kFull, leader);
 }
 
-// FP32 sum of the partitions in `parts` (ascending choice order), optional bias once, one bf16 round.
-__device__ __forceinline__ void reduce_token(const CommonParams& c, int t, unsigned parts, int my_part, const __nv_bfloat16* bias,
-                                             __nv_bfloat16* out) {
+// FP32 sum of the partitions in `parts` for the 16-byte column chunks `first`, `first + step`, ... of token t.
+// All partitions of a chunk are loaded before any is added, two chunks at a time.
+__device__ __forceinline__ void reduce_columns(const CommonParams& c, int t, unsigned parts, int my_part, const __nv_bfloat16* bias,
+                                               __nv_bfloat16* out, int first_base, int step) {
     const WindowLayout& L = c.layout;
     const int H = L.hidden, lane = threadIdx.x & 31;
     const int vecs = H / 8;
     const int64_t part_stride = L.max_tokens * int64_t(H) * 2;
     const char* row0 = window(c, c.rank) + L.ret_offset + int64_t(t) * H * 2;
-    for (int col = lane; col < vecs; col += 64) {
-        const bool two = col + 32 < vecs;
+    // `base` is the same for every lane of the warp (the loop holds warp shuffles); lanes past the row's end idle
+    for (int base = first_base; base < vecs; base += 2 * step) {
+        const int col = base + lane;
+        const bool one = col < vecs, two = col + step < vecs;
         float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         unsigned left = parts;
         while (left) {
-            int part[4];
-            int4 d0[4], d1[4];
+            int part[8];
+            int4 d0[8], d1[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const int k = left ? __ffs(left) - 1 : -1;
                 if (left) left &= left - 1;
                 part[j] = __shfl_sync(kFull, my_part, k < 0 ? 0 : k);
                 if (k < 0) part[j] = -1;
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 if (part[j] >= 0) {
                     const int4* src = reinterpret_cast<const int4*>(row0 + part[j] * part_stride);
-                    d0[j] = ld_cg_v4(src + col);
-                    if (two) d1[j] = ld_cg_v4(src + col + 32);
+                    if (one) d0[j] = ld_cg_v4(src + col);
+                    if (two) d1[j] = ld_cg_v4(src + col + step);
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 if (part[j] >= 0) {
-                    accumulate8(a0, d0[j]);
+                    if (one) accumulate8(a0, d0[j]);
                     if (two) accumulate8(a1, d1[j]);
                 }
             }
         }
         if (bias != nullptr) {
             const int4* b = reinterpret_cast<const int4*>(bias + int64_t(t) * H);
-            accumulate8(a0, ld_nc_v4(b + col));
-            if (two) accumulate8(a1, ld_nc_v4(b + col + 32));
+            if (one) accumulate8(a0, ld_nc_v4(b + col));
+            if (two) accumulate8(a1, ld_nc_v4(b + col + step));
         }
         int4* o = reinterpret_cast<int4*>(out + int64_t(t) * H);
-        o[col] = pack8(a0);
-        if (two) o[col + 32] = pack8(a1);
+        if (one) o[col] = pack8(a0);
+        if (two) o[col + step] = pack8(a1);
     }
 }
 
-// Reduce warps of the combine kernel: token t is summed once every partition it expects carries this combine's tag.
-__device__ void combine_reduce_role(const CombineParams& p) {
+// Reduce warps of the combine kernel.  They form groups of `reduce_group` warps; a group sums ONE source token at a
+// time, each lane its own column chunks, so that a token that has just become complete is finished in a few
+// microseconds (what is left of the kernel after the last row has landed is one such token per group).  The group's
+// first warp waits (bounded) until every partition the token expects carries this combine's tag and releases the
+// others through the group's named barrier.
+__device__ void combine_reduce_role(const CombineParams& p, int* abort_word) {
     const WindowLayout& L = p.c.layout;
     const int K = L.topk, Le = L.local_experts, E = int(L.num_experts);
     const int lane = threadIdx.x & 31;
-    const int RW = (blockDim.x >> 5) - p.push_warps;
-    const int gw = blockIdx.x * RW + ((threadIdx.x >> 5) - p.push_warps), GW = gridDim.x * RW;
+    const int RW = (blockDim.x >> 5) - p.push_warps - 1;  // one warp publishes flags
+    const int rwarp = (threadIdx.x >> 5) - p.push_warps - 1;
+    const int G = p.reduce_group < 1 ? 1 : (p.reduce_group > RW ? RW : p.reduce_group);
+    const int groups = RW / G, g = rwarp / G, wi = rwarp % G;
+    if (g >= groups) return;  // warps that do not fill a group idle
     const StatusRef status = status_of(p.c);
     const uint32_t tag = combine_tag(p.epoch);
     const uint32_t* flag_base = reinterpret_cast<const uint32_t*>(window(p.c, p.c.rank) + L.ret_flag_offset);
     const float* ret_w = reinterpret_cast<const float*>(window(p.c, p.c.rank) + L.ret_w_offset);
-    for (int t = gw; t < p.tokens; t += GW) {
+    for (int t = blockIdx.x * groups + g; t < p.tokens; t += gridDim.x * groups) {
         bool valid;
         int dest;
         const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
         const int my_part = L.rank_indexed ? dest : lane;
-        const bool mine = (parts >> lane) & 1u;
         if (parts != 0) {
-            const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
-            const uint64_t start = global_timer_ns();
-            uint32_t spins = 0;
-            bool arrived = false;
-            for (;;) {
-                const bool here = !mine || ld_acquire_sys_u32(flag) == tag;
-                arrived = __all_sync(kFull, here);
-                if (arrived) break;
-                __nanosleep(100);
-                if ((++spins & 15u) == 0u && __any_sync(kFull, global_timer_ns() - start > p.c.timeout_ns)) break;
+            if (wi == 0) {
+                const bool mine = (parts >> lane) & 1u;
+                const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
+                const uint64_t start = global_timer_ns();
+                uint32_t spins = 0;
+                bool arrived = false;
+                for (;;) {
+                    const bool here = !mine || ld_relaxed_sys_u32(flag) == tag;
+                    arrived = __all_sync(kFull, here);
+                    if (arrived) break;
+                    __nanosleep(200);
+                    if ((++spins & 15u) == 0u && __any_sync(kFull, global_timer_ns() - start > p.c.timeout_ns)) break;
+                }
+                // the polls were relaxed; one acquiring load of each flag orders the rows behind them
+                if (arrived && mine) (void)ld_acquire_sys_u32(flag);
+                __syncwarp();
+                if (!arrived && lane == 0) {
+                    report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
+                    *(volatile int*)abort_word = 1;  // a peer never delivered: stop reducing, the host reports the status
+                }
             }
-            __syncwarp();
-            if (!arrived) {
-                if (lane == 0) report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
-                return;  // a peer never delivered: stop reducing, the host reports the status
-            }
+            // named barrier 1 + g: this group's reduce warps only
+            if (G > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(G * 32) : "memory");
+            if (*(volatile int*)abort_word) return;
         }
-        reduce_token(p.c, t, parts, my_part, p.bias, p.out);
-        if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+        reduce_columns(p.c, t, parts, my_part, p.bias, p.out, wi * 32, G * 32);
+        if (wi == 0 && p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
     }
 }
 
 __device__ void combine_body(const CombineParams& p) {
     extern __shared__ __align__(128) char s_ring[];
-    __shared__ int s_enter;
+    __shared__ int s_enter, s_abort;
     const WindowLayout& L = p.c.layout;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const StatusRef status = status_of(p.c);
     int* ctrl = ctrl_words(p.c);
-    if (threadIdx.x == 0) s_enter = 1;
+    // the flag board sits behind the transfer rings (plan_ring leaves room for it)
+    FlagBoard* board = reinterpret_cast<FlagBoard*>(
+        (reinterpret_cast<uintptr_t>(s_ring + (align_up(int64_t(L.hidden) * 2, 128) + 8) * int64_t(p.push_warps) * p.stages) + 15) & ~uintptr_t(15));
+    if (threadIdx.x == 0) {
+        s_enter = 1;
+        s_abort = 0;
+    }
+    if (threadIdx.x < kMaxPushWarps) board->completed[threadIdx.x] = board->published[threadIdx.x] = board->finished[threadIdx.x] = 0;
     __syncthreads();
     if (p.wait_epoch != 0) {
         // Every peer has finished reading what the previous combine left in its return area.
@@ -932,11 +1049,16 @@ __device__ void combine_body(const CombineParams& p) {
         }
         __syncthreads();
     }
+    if (p.trace != nullptr && threadIdx.x == 0) atomicMin(p.trace, global_timer_ns());
     if (s_enter) {
-        if (warp < p.push_warps)
-            combine_push_role(p, s_ring);
+        const int role = warp < p.push_warps ? 1 : warp == p.push_warps ? 2 : 3;
+        if (role == 1)
+            combine_push_role(p, s_ring, board);
+        else if (role == 2)
+            combine_publish_role(p, board);
         else
-            combine_reduce_role(p);
+            combine_reduce_role(p, &s_abort);
+        if (p.trace != nullptr && lane == 0) atomicMax(p.trace + role, global_timer_ns());
     }
     // The last block out tells every peer that this rank is done with the combine (nobody waits here).
     __threadfence_system();
@@ -960,7 +1082,7 @@ __device__ void reduce_body(const ReduceParams& p) {
         bool valid;
         int dest;
         const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
-        reduce_token(p.c, t, parts, L.rank_indexed ? dest : lane, p.bias, p.out);
+        reduce_columns(p.c, t, parts, L.rank_indexed ? dest : lane, p.bias, p.out, 0, 32);
         if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
     }
 }

@@ -87,9 +87,10 @@ struct PullParams {
 
 enum PushMode : int { kPushCompact = 0, kPushExpanded = 1, kPushExpandedReduce = 2 };
 
-// One launch per combine.  Every CTA holds `push_warps` transfer warps (shared-memory ring, bulk copies) and
-// reduce warps.  Transfer warps return this rank's expert outputs to the source ranks' return partitions and,
-// once a row's bulk store has completed, publish the combine's tag in the row's arrival flag.  Reduce warps
+// One launch per combine.  Every CTA holds `push_warps` transfer warps (shared-memory ring, bulk copies), one
+// publisher warp and reduce warps.  Transfer warps return this rank's expert outputs to the source ranks'
+// return partitions; once a row's bulk store has completed the publisher warp writes the combine's tag into
+// the row's arrival flag (one system-scope release per sweep, off the transfer warps' path).  Reduce warps
 // walk this rank's own source tokens, wait (bounded) until every partition a token expects carries the tag,
 // and write the FP32 sum.  No barrier sits between the two: the only cross-rank waits are the flags.
 struct CombineParams {
@@ -113,6 +114,12 @@ struct CombineParams {
     int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank
     uint64_t epoch;       // signalled to every peer when this rank's pushes and reduction are done
     uint64_t wait_epoch;  // peers must have signalled this much before their return area is overwritten (0: nothing to wait for)
+    int reduce_group;     // reduce warps that share one source token (1 .. reduce warps per CTA)
+    int store_depth;      // bulk stores a transfer warp may have pending before it waits (2, 4, 6, 8 or 12; else 4)
+    // Optional diagnostics (null = off): [0] earliest start, [1] latest end of the transfer warps, [2] of the
+    // publisher warps, [3] of the reduce warps, as %globaltimer nanoseconds.  A kernel profiler cannot be
+    // attached to a multi-process run, and events cannot see inside one launch.
+    unsigned long long* trace;
 };
 
 // Source-side reduction alone, for a combine whose rows were pushed by another kernel (the scatter epilogue of

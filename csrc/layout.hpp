@@ -47,6 +47,8 @@ struct WindowLayout {
     int64_t counts_in_stride;
     int64_t routing_in_offset;   // [2] i32[R][Tmax][K] every source's routing, written by the sources
     int64_t routing_in_stride;
+    int64_t chunks_in_offset;    // [2] i32[R][ceil(Tmax/32)] rows each source sends here per chunk of 32 of its tokens
+    int64_t chunks_in_stride;    //     (written by the sources; turned into an exclusive prefix by the receiver)
     int64_t stage_rows_offset;   // [2] u8[Tmax][wire_row_bytes] staged tokens, pulled by the receivers
     int64_t stage_rows_stride;
     int ret_parts;               // P: return partitions per token
@@ -68,7 +70,9 @@ struct WindowLayout {
     NEP_HD int64_t ctrl_expert_offsets() const { return ctrl_recv_prefix() + ranks + 1; }      // i32[L+1]
     NEP_HD int64_t ctrl_expert_counts() const { return ctrl_expert_offsets() + local_experts + 1; }  // i32[L]
     NEP_HD int64_t ctrl_src_tokens() const { return ctrl_expert_counts() + local_experts; }    // i32[R]
-    NEP_HD int64_t ctrl_ints() const { return ctrl_src_tokens() + ranks; }
+    NEP_HD int64_t ctrl_chunk_acc() const { return ctrl_src_tokens() + ranks; }                // i32[R][chunks_per_rank()]
+    NEP_HD int64_t ctrl_ints() const { return ctrl_chunk_acc() + int64_t(ranks) * chunks_per_rank(); }
+    NEP_HD int64_t chunks_per_rank() const { return (max_tokens + 31) / 32; }
 
     NEP_HD int64_t row_bytes() const { return wire_row_bytes(hidden, topk); }
     NEP_HD int64_t msg_ints() const { return count_msg_ints(local_experts); }
@@ -102,6 +106,8 @@ struct WindowLayout {
         w.counts_in_offset = take(2 * w.counts_in_stride);
         w.routing_in_stride = align_up(int64_t(ranks) * max_tokens * topk * 4, kRegionAlign);
         w.routing_in_offset = take(2 * w.routing_in_stride);
+        w.chunks_in_stride = align_up(int64_t(ranks) * w.chunks_per_rank() * 4, kRegionAlign);
+        w.chunks_in_offset = take(2 * w.chunks_in_stride);
         w.stage_rows_stride = align_up(max_tokens * w.row_bytes(), kRegionAlign);
         w.stage_rows_offset = take(2 * w.stage_rows_stride);
         // One row per (token, expert rank) comes back when the buffer pre-reduces per rank: min(R, K) partitions

@@ -93,12 +93,26 @@ std::string PeerWindow::export_handle() {
     return std::string(reinterpret_cast<const char*>(&h), sizeof(h));
 }
 
-void PeerWindow::import_handles(const std::vector<std::string>& handles) {
+void PeerWindow::import_handles(const std::vector<std::string>& handles, const std::vector<int>& peer_devices) {
     if (closed_ || connected_) throw std::runtime_error("peer window already connected or closed");
     if (int(handles.size()) != world_) throw std::invalid_argument("need one IPC handle per rank");
+    if (!peer_devices.empty() && int(peer_devices.size()) != world_) throw std::invalid_argument("need one device ordinal per rank");
     try {
         for (int p = 0; p < world_; ++p) {
             if (p == rank_) continue;
+            // Where the peer's GPU is visible to this process, check before mapping that it is another GPU and that
+            // this GPU may load from, store to and bulk-copy into it (same role as the reference's checks,
+            // csrc/peer.cu:95-126).  A peer GPU outside this process's visible set can only be judged by the mapping call.
+            const int peer_device = peer_devices.empty() ? -1 : peer_devices[p];
+            if (peer_device >= 0) {
+                int can = 0, supported = 0;
+                if (peer_device != device_) {
+                    check(cudaDeviceCanAccessPeer(&can, device_, peer_device), "cudaDeviceCanAccessPeer");
+                    check(cudaDeviceGetP2PAttribute(&supported, cudaDevP2PAttrAccessSupported, device_, peer_device), "cudaDeviceGetP2PAttribute");
+                }
+                const std::string problem = peer_access_error(rank_, p, device_, peer_device, can != 0, supported != 0);
+                if (!problem.empty()) throw std::runtime_error(problem);
+            }
             if (handles[p].size() != sizeof(cudaIpcMemHandle_t)) throw std::invalid_argument("IPC handle must be 64 bytes");
             cudaIpcMemHandle_t h;
             std::memcpy(&h, handles[p].data(), sizeof(h));
@@ -106,17 +120,6 @@ void PeerWindow::import_handles(const std::vector<std::string>& handles) {
             check(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
             peers_[p] = mapped;
             imported_[p] = true;
-            // The mapping alone proves little: check where the memory lives and that this GPU may load from,
-            // store to and bulk-copy into it (same role as the reference's checks, csrc/peer.cu:95-126).
-            cudaPointerAttributes where{};
-            check(cudaPointerGetAttributes(&where, mapped), "cudaPointerGetAttributes(peer window)");
-            int can = 0, supported = 0;
-            if (where.device != device_) {
-                check(cudaDeviceCanAccessPeer(&can, device_, where.device), "cudaDeviceCanAccessPeer");
-                check(cudaDeviceGetP2PAttribute(&supported, cudaDevP2PAttrAccessSupported, device_, where.device), "cudaDeviceGetP2PAttribute");
-            }
-            const std::string problem = peer_access_error(rank_, p, device_, where.device, can != 0, supported != 0);
-            if (!problem.empty()) throw std::runtime_error(problem);
         }
     } catch (...) {
         for (int p = 0; p < world_; ++p)

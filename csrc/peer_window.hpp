@@ -34,8 +34,9 @@ public:
 
     // 64 raw bytes of the CUDA IPC memory handle of the local window.
     std::string export_handle();
-    // Map every peer's window (index = rank; the own entry is ignored) and check P2P access.
-    void import_handles(const std::vector<std::string>& handles);
+    // Map every peer's window (index = rank; the own entry is ignored).  `peer_devices[p]` is the CUDA ordinal of
+    // rank p's GPU in THIS process (-1 when it is not visible here); visible peers are checked for P2P access first.
+    void import_handles(const std::vector<std::string>& handles, const std::vector<int>& peer_devices = {});
     // Same-process alternative: use other PeerWindow objects (one per logical rank) as peers.
     void adopt_peers(const std::vector<PeerWindow*>& group);
     // Two-phase teardown: every importer unmaps first; only then may owners free.

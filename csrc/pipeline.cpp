@@ -56,6 +56,16 @@ struct PhaseMarks {
 };
 PhaseMarks g_marks;
 
+// In-kernel time stamps of the combine kernel (see CombineParams::trace): a small device buffer, reset before
+// every traced combine and read on request.
+struct CombineTrace {
+    bool enabled = false;
+    at::Tensor words;  // uint64 x 4 as int64
+    int depth = 0;     // 0 = kernel default
+    int group = 0;     // 0 = default reduce group size
+};
+CombineTrace g_trace;
+
 // Single-launch path for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
 // stage, peer barrier and pull as one cooperative launch; `blocks` bounds its grid (every block must be
 // resident at once and spins on one word while the last block runs the peer barrier).  Defaults come from
@@ -532,7 +542,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     }
     std::vector<CombineParams> params(n);
     std::vector<at::Tensor> keep;
-    TORCH_CHECK(ring.stages >= 2 && ring.warps < kCombineThreads / 32, "combine ring plan out of range");
+    TORCH_CHECK(ring.stages >= 2 && ring.warps >= 1 && ring.warps <= 8, "combine ring plan out of range");
     {
         c10::cuda::CUDAStreamGuard pool(consumer);
         for (int i = 0; i < n; ++i) {
@@ -562,6 +572,16 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             p.sum_all_choices = (expand && !allow_multiple_reduction) ? 1 : 0;
             p.epoch = epochs.epoch;
             p.wait_epoch = epochs.wait_epoch;
+            p.store_depth = g_trace.depth;
+            {
+                // Reduce warps per token: all of a CTA's reduce warps split evenly in two groups by default.
+                const int reduce_warps = kCombineThreads / 32 - ring.warps - 1;
+                p.reduce_group = g_trace.group > 0 ? g_trace.group : std::max(1, reduce_warps / 2);
+            }
+            if (g_trace.enabled && n == 1) {
+                if (!g_trace.words.defined()) g_trace.words = at::empty({4}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
+                p.trace = reinterpret_cast<unsigned long long*>(g_trace.words.data_ptr<int64_t>());
+            }
             TORCH_CHECK(p.sum_all_choices == 0 || L.ret_parts == L.topk, "this buffer's return area holds one partition per rank only");
         }
     }
@@ -572,14 +592,19 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             max_transfers = std::max<int64_t>(max_transfers, expand && !allow_multiple_reduction ? capacity[i] : meta[i][0].size(0));
             max_tokens_now = std::max<int64_t>(max_tokens_now, meta[i][5].size(0));
         }
-        const int reduce_warps = kCombineThreads / 32 - ring.warps;
-        // Every block holds transfer warps and reduce warps: enough blocks for the larger of the two jobs.
-        const int64_t wanted = std::max<int64_t>((max_transfers + ring.warps - 1) / ring.warps, (max_tokens_now + reduce_warps - 1) / reduce_warps);
+        // Every block holds transfer warps and a group of reduce warps that sums one token at a time: enough blocks
+        // for the larger of the two jobs.
+        const int groups = std::max(1, (kCombineThreads / 32 - ring.warps - 1) / params[0].reduce_group);
+        const int64_t wanted = std::max<int64_t>((max_transfers + ring.warps - 1) / ring.warps, (max_tokens_now + groups - 1) / groups);
         // A whole logical group in one launch waits on itself: all its blocks must be resident (cooperative launch).
         const bool group_launch = n > 1;
         const int64_t cap = group_launch ? std::min<int64_t>(num_sms, lim.sms / n) : num_sms;
         const int grid = int(std::max<int64_t>(1, std::min<int64_t>(cap, wanted)));
         const CombineParams* dev = upload(params, keep, cs);
+        if (g_trace.enabled && n == 1) {
+            const int64_t init[4] = {INT64_MAX, 0, 0, 0};  // [0] takes the minimum, the others the maximum
+            cuda_check(cudaMemcpyAsync(g_trace.words.data_ptr(), init, sizeof(init), cudaMemcpyHostToDevice, cs), "trace reset");
+        }
         g_marks.mark("begin", cs);
         PeerWindow::launches += 1;
         cuda_check(launch_combine(dev, LaunchShape{grid, n}, ring.smem_bytes, cs, group_launch), "combine launch");
@@ -652,6 +677,22 @@ void set_fused_limits(int64_t dispatch_tokens, int64_t blocks) {
 }
 
 void set_phase_timing(bool enabled) { g_marks.enabled = enabled; }
+
+void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group) {
+    g_trace.enabled = enabled;
+    g_trace.depth = int(store_depth);
+    g_trace.group = int(reduce_group);
+}
+
+std::vector<double> take_combine_trace() {
+    std::vector<double> out;
+    if (!g_trace.words.defined()) return out;
+    const at::Tensor host = g_trace.words.cpu();  // synchronises with the stream that ran the combine
+    const int64_t* w = host.data_ptr<int64_t>();
+    if (w[0] == INT64_MAX) return out;
+    for (int i = 1; i < 4; ++i) out.push_back(w[i] > w[0] ? double(w[i] - w[0]) * 1e-3 : 0.0);
+    return out;
+}
 
 std::vector<std::pair<std::string, double>> take_phase_timings() {
     std::vector<std::pair<std::string, double>> out;

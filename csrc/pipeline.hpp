@@ -64,6 +64,12 @@ FusedLimits fused_limits();
 // Negative token values / blocks < 1 leave the respective setting unchanged.
 void set_fused_limits(int64_t dispatch_tokens, int64_t blocks);
 
+// In-kernel time stamps of the next combines of this process (single-rank calls): microseconds from the
+// kernel's first block to the end of its transfer warps, its flag publishers and its reduce warps.
+// `store_depth` (0 = default) sets how many bulk stores a transfer warp keeps pending, `reduce_group` (0 = default)
+// how many reduce warps share one source token.
+void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group);
+std::vector<double> take_combine_trace();
 void set_phase_timing(bool enabled);
 std::vector<std::pair<std::string, double>> take_phase_timings();
 

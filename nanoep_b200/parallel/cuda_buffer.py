@@ -152,7 +152,9 @@ class CudaBuffer:
         if not errors:
 
             def connect():
-                self._window.import_handles(handles)
+                # each peer's GPU as this process sees it (by UUID; -1 when it is outside the visible set)
+                visible = {str(torch.cuda.get_device_properties(i).uuid): i for i in range(torch.cuda.device_count())}
+                self._window.import_handles(handles, [visible.get(uuid, -1) for uuid in self._gpu_uuids])
                 self._comm_stream = torch.cuda.Stream(device=self._device)
 
             _, errors = bootstrap.collective_step(group, "import/stream", connect)

@@ -35,12 +35,15 @@ def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_expe
 
     out = {}
     out["signal_offset"] = take(32 * 8)
-    ctrl_ints = 16 + (ranks + num_experts) + ranks + local + (ranks + 1) + (local + 1) + local + ranks
+    chunks = (max_tokens + 31) // 32  # rows are planned per chunk of 32 source tokens
+    ctrl_ints = 16 + (ranks + num_experts) + ranks + local + (ranks + 1) + (local + 1) + local + ranks + ranks * chunks
     out["ctrl_offset"] = take(ctrl_ints * 4)
     out["counts_in_stride"] = align(ranks * count_message_ints(local) * 4, region)
     out["counts_in_offset"] = take(2 * out["counts_in_stride"])
     out["routing_in_stride"] = align(ranks * max_tokens * topk * 4, region)
     out["routing_in_offset"] = take(2 * out["routing_in_stride"])
+    out["chunks_in_stride"] = align(ranks * chunks * 4, region)
+    out["chunks_in_offset"] = take(2 * out["chunks_in_stride"])
     out["stage_rows_stride"] = align(max_tokens * wire_row_bytes(hidden, topk), region)
     out["stage_rows_offset"] = take(2 * out["stage_rows_stride"])
     # return area: one copy; P partitions of [Tmax, H] bf16, a u32 arrival flag per (partition, token), fp32 weights [Tmax, K]

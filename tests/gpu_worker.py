@@ -192,10 +192,10 @@ def bootstrap_faults(group, rank, world):
         def __getattr__(self, name):
             return getattr(self._inner, name)
 
-        def import_handles(self, handles):
+        def import_handles(self, handles, peer_devices=()):
             if rank == 0:
                 raise RuntimeError("injected import failure")
-            return self._inner.import_handles(handles)
+            return self._inner.import_handles(handles, list(peer_devices))
 
     class PatchedBackend:
         def __init__(self, inner):

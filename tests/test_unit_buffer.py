@@ -62,7 +62,7 @@ class FakeWindow:
         self.log.append((self.rank, "export"))
         return bytes([self.rank]) * 64
 
-    def import_handles(self, handles):
+    def import_handles(self, handles, peer_devices=()):
         assert [h[0] for h in handles] == list(range(len(handles))) and all(len(h) == 64 for h in handles)
         if self.fail_at == "import":
             raise RuntimeError("import boom")
