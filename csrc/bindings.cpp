@@ -21,6 +21,7 @@ struct HandleState {
 py::dict layout_dict(const nep::WindowLayout& w) {
     py::dict d;
     d["signal_offset"] = w.signal_offset;
+    d["data_signal_offset"] = w.data_signal_offset;
     d["ctrl_offset"] = w.ctrl_offset;
     d["counts_in_offset"] = w.counts_in_offset;
     d["counts_in_stride"] = w.counts_in_stride;
@@ -175,6 +176,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("set_combine_trace", &nep::set_combine_trace, py::arg("enabled"), py::arg("store_depth") = 0, py::arg("reduce_group") = 0);
     m.def("take_combine_trace", &nep::take_combine_trace);
+    m.def("take_stage_trace", &nep::take_stage_trace);
     m.def("take_phase_timings", &nep::take_phase_timings);
     m.def("launch_count", [] { return PeerWindow::launches; });
     m.def("format_status", &nep::format_status);

@@ -96,31 +96,16 @@ __device__ bool stage_body(const StageParams& p) {
     const int64_t rb = L.row_bytes();
     const int vecs = H / 8;  // 16-byte chunks per row
 
-    // Work item = one quarter of a token row, so that even a few thousand tokens spread over the whole
-    // grid and every lane keeps up to eight 16-byte loads in flight.  The warp that takes quarter 0
-    // also handles the token's gate weights and routing.
-    constexpr int kParts = 4;
-    const int per_part = (vecs + kParts - 1) / kParts;
-    for (int item = gw; item < p.tokens * kParts; item += GW) {
-        const int t = item / kParts, q = item % kParts;
-        const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
-        int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
-        const int end = p.skip_copy ? 0 : min(vecs, (q + 1) * per_part);
-        for (int i = q * per_part + lane; i < end; i += 256) {
-            int4 v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (i + j * 32 < end) v[j] = ld_nc_v4(src + i + j * 32);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (i + j * 32 < end) dst[i + j * 32] = v[j];
-        }
-        if (q != 0) continue;
-        if (lane < K) {
-            const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
-            reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
-        }
-        if (p.fresh) {
+    auto stamp = [&](int slot) {
+        if (p.trace != nullptr && tid == 0) atomicMax(p.trace + slot, global_timer_ns());
+    };
+    if (p.trace != nullptr && tid == 0) atomicMin(p.trace, global_timer_ns());
+
+    // ---- fresh dispatch, step 1: snapshot, validate, publish and count the routing (one warp per token).  The
+    // counts are what every rank and the host wait for, so they go first; the rows follow underneath the exchange.
+    bool runs_tail = false;
+    if (p.fresh) {
+        for (int t = gw; t < p.tokens; t += GW) {
             int e = -1;
             bool valid = false;
             if (lane < K) {
@@ -151,14 +136,50 @@ __device__ bool stage_body(const StageParams& p) {
                 if (goes) atomicAdd(ctrl + L.ctrl_chunk_acc() + int64_t(lane) * L.chunks_per_rank() + (t >> 5), 1);
             }
         }
-    }
-
-    if (p.fresh) {
         __syncthreads();
         for (int i = tid; i < R + E; i += blockDim.x)
             if (s_counts[i] != 0) atomicAdd(&count_acc[i], s_counts[i]);
+        runs_tail = take_last_ticket(ctrl + WindowLayout::kTicketStage);
+        stamp(1);
     }
-    if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
+
+    // ---- rows: x and gate weights into this rank's staging area.  Work item = one quarter of a token row, so that
+    // even a few thousand tokens spread over the whole grid and every lane keeps up to eight 16-byte loads in flight.
+    if (!p.skip_copy) {
+        constexpr int kParts = 4;
+        const int per_part = (vecs + kParts - 1) / kParts;
+        for (int item = gw; item < p.tokens * kParts; item += GW) {
+            const int t = item / kParts, q = item % kParts;
+            const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
+            int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
+            const int end = min(vecs, (q + 1) * per_part);
+            for (int i = q * per_part + lane; i < end; i += 256) {
+                int4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (i + j * 32 < end) v[j] = ld_nc_v4(src + i + j * 32);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (i + j * 32 < end) dst[i + j * 32] = v[j];
+            }
+            if (q == 0 && lane < K) {
+                const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
+                reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
+            }
+        }
+    }
+    if (p.fresh) {
+        // The block that finishes its rows last tells every peer that this rank's rows are staged; the receivers'
+        // pull waits for these signals, nobody waits here.
+        if (take_last_ticket(ctrl + WindowLayout::kTicketCopy)) {
+            if (tid == 0) ctrl[WindowLayout::kTicketCopy] = 0;
+            __threadfence_system();
+            __syncthreads();
+            if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, R, L.data_signal_offset, p.epoch);
+        }
+        stamp(2);
+        if (!runs_tail) return false;
+    } else if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
         if (!p.fused) return false;
         return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
     }
@@ -195,6 +216,7 @@ __device__ bool stage_body(const StageParams& p) {
         if (lane == 0) s_ok = ok;
     }
     __syncthreads();
+    stamp(3);
     if (p.fused) {
         if (tid == 0) publish_go(ctrl, p.epoch, s_ok != 0);
         return s_ok != 0;
@@ -281,6 +303,7 @@ __device__ bool stage_body(const StageParams& p) {
         p.mailbox[0] = s_total[0];
         __threadfence_system();
     }
+    stamp(4);
     return true;
 }
 
@@ -476,6 +499,17 @@ __device__ void pull_body(const PullParams& p) {
     const int MW = K + 2;
     Ring ring = make_ring(s_ring, wpb, p.stages, rb);
     const int S = p.stages;
+    if (p.data_epoch != 0) {
+        // A fresh dispatch stages its rows underneath the count exchange: every source signals when its rows are in place.
+        __shared__ int s_staged;
+        if (warp == 0) {
+            const bool ok = peer_wait_warp(p.c.peers, p.c.rank, R, L.data_signal_offset, p.data_epoch, p.c.timeout_ns, status, kTagPull);
+            if (lane == 0) s_staged = ok;
+        }
+        __syncthreads();
+        if (!s_staged) return;
+        fence_proxy_async();
+    }
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
     const bool slot_order = p.slot_src != nullptr;
     const int n_items = slot_order ? p.capacity : walk.items;
@@ -669,11 +703,11 @@ constexpr int kFlagRing = 32;  // entries per transfer warp
 constexpr int kMaxPushWarps = 8;
 __device__ __forceinline__ void bulk_wait_depth(int depth) {
     switch (depth) {
-        case 2: bulk_wait<2>(); break;
+        case 4: bulk_wait<4>(); break;
         case 6: bulk_wait<6>(); break;
         case 8: bulk_wait<8>(); break;
         case 12: bulk_wait<12>(); break;
-        default: bulk_wait<4>(); break;
+        default: bulk_wait<2>(); break;
     }
 }
 struct FlagBoard {
@@ -765,7 +799,7 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
     const int S = p.stages;
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
     const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
-    const int depth = (p.store_depth == 2 || p.store_depth == 6 || p.store_depth == 8 || p.store_depth == 12) ? p.store_depth : 4;
+    const int depth = (p.store_depth == 4 || p.store_depth == 6 || p.store_depth == 8 || p.store_depth == 12) ? p.store_depth : 2;
     FlagWriter flags{board, warp, 0, depth, p.c.timeout_ns};
 
     if (p.mode == kPushExpandedReduce) {
@@ -1060,8 +1094,9 @@ __device__ void combine_body(const CombineParams& p) {
             combine_reduce_role(p, &s_abort);
         if (p.trace != nullptr && lane == 0) atomicMax(p.trace + role, global_timer_ns());
     }
-    // The last block out tells every peer that this rank is done with the combine (nobody waits here).
-    __threadfence_system();
+    // The last block out tells every peer that this rank is done with the combine (nobody waits here).  Rows and
+    // flags are out already (completed bulk groups, the publishers' fences); the ticket orders this block's reads of
+    // the return area before the signal that lets peers overwrite it.
     if (!take_last_ticket(ctrl + WindowLayout::kTicketCombine)) return;
     if (threadIdx.x == 0) ctrl[WindowLayout::kTicketCombine] = 0;
     __threadfence_system();

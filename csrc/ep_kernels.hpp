@@ -50,6 +50,9 @@ struct StageParams {
     int64_t* expert_counts;     // [L]
     int64_t* expert_offsets;    // [L+1]
     volatile int64_t* mailbox;  // mapped host: [0]=N, [1]=C (negative = failure)
+    // Optional diagnostics (null = off), %globaltimer nanoseconds: [0] earliest start, [1] routing counted,
+    // [2] rows staged, [3] peer barrier passed, [4] end of the tail block.
+    unsigned long long* trace;
 };
 
 struct PlanParams {
@@ -82,6 +85,7 @@ struct PullParams {
     // Rows whose source is this rank may be read from the caller's tensors instead of the staged copy.
     const __nv_bfloat16* x_local;  // [T,H] or null
     const float* w_local;          // [T,K] or null
+    uint64_t data_epoch;  // fresh dispatch: wait until every source has signalled its staged rows with this epoch (0: no wait)
     int* tile_ready;  // optional: [C/128] counters, +1 per expert-major row (data or zero padding) once it is in memory
 };
 
@@ -115,7 +119,7 @@ struct CombineParams {
     uint64_t epoch;       // signalled to every peer when this rank's pushes and reduction are done
     uint64_t wait_epoch;  // peers must have signalled this much before their return area is overwritten (0: nothing to wait for)
     int reduce_group;     // reduce warps that share one source token (1 .. reduce warps per CTA)
-    int store_depth;      // bulk stores a transfer warp may have pending before it waits (2, 4, 6, 8 or 12; else 4)
+    int store_depth;      // bulk stores a transfer warp may have pending before it waits (2, 4, 6, 8 or 12; anything else means 2)
     // Optional diagnostics (null = off): [0] earliest start, [1] latest end of the transfer warps, [2] of the
     // publisher warps, [3] of the reduce warps, as %globaltimer nanoseconds.  A kernel profiler cannot be
     // attached to a multi-process run, and events cannot see inside one launch.

@@ -42,6 +42,7 @@ struct WindowLayout {
     // Region offsets (bytes from the window base).  Regions marked [2] hold two parity copies,
     // `*_stride` apart.
     int64_t signal_offset;       // u64[kMaxRanks]   epoch written by each peer
+    int64_t data_signal_offset;  // u64[kMaxRanks]   epoch of the fresh dispatch whose rows peer p has finished staging
     int64_t ctrl_offset;         // local scratch: tickets, count accumulators, cursors, prefixes
     int64_t counts_in_offset;    // [2] i32[R][2+L]  count messages written by the sources
     int64_t counts_in_stride;
@@ -101,6 +102,7 @@ struct WindowLayout {
             return here;
         };
         w.signal_offset = take(kMaxRanks * 8);
+        w.data_signal_offset = take(kMaxRanks * 8);
         w.ctrl_offset = take(w.ctrl_ints() * 4);
         w.counts_in_stride = align_up(int64_t(ranks) * w.msg_ints() * 4, kRegionAlign);
         w.counts_in_offset = take(2 * w.counts_in_stride);

@@ -61,6 +61,7 @@ PhaseMarks g_marks;
 struct CombineTrace {
     bool enabled = false;
     at::Tensor words;  // uint64 x 4 as int64
+    at::Tensor stage_words;  // uint64 x 5 as int64 (stage kernel of a fresh dispatch)
     int depth = 0;     // 0 = kernel default
     int group = 0;     // 0 = default reduce group size
 };
@@ -314,6 +315,11 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
                 p.expert_offsets = m[2].data_ptr<int64_t>();
                 wins[i]->arm_mailbox();
                 p.mailbox = wins[i]->mailbox_device();
+                if (g_trace.enabled && n == 1) {
+                    if (!g_trace.stage_words.defined())
+                        g_trace.stage_words = at::empty({5}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
+                    p.trace = reinterpret_cast<unsigned long long*>(g_trace.stage_words.data_ptr<int64_t>());
+                }
             }
         }
     }
@@ -328,6 +334,10 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         c10::cuda::CUDAStreamGuard on_comm(s.work);
         for (int i = 0; i < n; ++i) stage[i].fused = fuse_small ? 1 : 0;
         stage_dev = upload(stage, keep, cs);
+        if (fresh && g_trace.enabled && n == 1) {
+            const int64_t init[5] = {INT64_MAX, 0, 0, 0, 0};
+            cuda_check(cudaMemcpyAsync(g_trace.stage_words.data_ptr(), init, sizeof(init), cudaMemcpyHostToDevice, cs), "trace reset");
+        }
         g_marks.mark("begin", cs);
         if (!fuse_small) {
             PeerWindow::launches += 1;
@@ -383,6 +393,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.meta = fresh ? reinterpret_cast<const int*>(static_cast<char*>(wins[i]->base()) + L.meta_scratch_offset) : m[0].data_ptr<int>();
             p.rows = int(N);
             p.parity = parity[i];
+            p.data_epoch = fresh ? stage[i].epoch : 0;
             p.expand = expand;
             p.zero_padding = zero_padding;
             p.write_meta = fresh;
@@ -574,9 +585,9 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             p.wait_epoch = epochs.wait_epoch;
             p.store_depth = g_trace.depth;
             {
-                // Reduce warps per token: all of a CTA's reduce warps split evenly in two groups by default.
-                const int reduce_warps = kCombineThreads / 32 - ring.warps - 1;
-                p.reduce_group = g_trace.group > 0 ? g_trace.group : std::max(1, reduce_warps / 2);
+                // Two reduce warps share a token by default (measured at 2 and 8 GPUs: one or two per token finish the
+                // kernel soonest; larger groups spend more on their barrier than they gain).
+                p.reduce_group = g_trace.group > 0 ? g_trace.group : 2;
             }
             if (g_trace.enabled && n == 1) {
                 if (!g_trace.words.defined()) g_trace.words = at::empty({4}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
@@ -682,6 +693,16 @@ void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group) 
     g_trace.enabled = enabled;
     g_trace.depth = int(store_depth);
     g_trace.group = int(reduce_group);
+}
+
+std::vector<double> take_stage_trace() {
+    std::vector<double> out;
+    if (!g_trace.stage_words.defined()) return out;
+    const at::Tensor host = g_trace.stage_words.cpu();
+    const int64_t* w = host.data_ptr<int64_t>();
+    if (w[0] == INT64_MAX) return out;
+    for (int i = 1; i < 5; ++i) out.push_back(w[i] > w[0] ? double(w[i] - w[0]) * 1e-3 : 0.0);
+    return out;
 }
 
 std::vector<double> take_combine_trace() {

@@ -70,6 +70,9 @@ void set_fused_limits(int64_t dispatch_tokens, int64_t blocks);
 // how many reduce warps share one source token.
 void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group);
 std::vector<double> take_combine_trace();
+// The same for the stage kernel of the last fresh dispatch: microseconds until the routing was counted, the rows
+// were staged, the peer barrier was passed and the tail block finished.
+std::vector<double> take_stage_trace();
 void set_phase_timing(bool enabled);
 std::vector<std::pair<std::string, double>> take_phase_timings();
 

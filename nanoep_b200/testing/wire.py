@@ -35,6 +35,7 @@ def window_regions(ranks: int, max_tokens: int, hidden: int, topk: int, num_expe
 
     out = {}
     out["signal_offset"] = take(32 * 8)
+    out["data_signal_offset"] = take(32 * 8)
     chunks = (max_tokens + 31) // 32  # rows are planned per chunk of 32 source tokens
     ctrl_ints = 16 + (ranks + num_experts) + ranks + local + (ranks + 1) + (local + 1) + local + ranks + ranks * chunks
     out["ctrl_offset"] = take(ctrl_ints * 4)
