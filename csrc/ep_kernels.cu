@@ -1217,6 +1217,20 @@ __device__ void barrier_body(const BarrierParams& p) {
                       kTagBarrier);
 }
 
+// Test utility: holds a stream until a word in pinned host memory becomes non-zero (bounded; gate[1] = 1 when the wait
+// ran out).  The poll is a system-scope load: it must not be served from a cache on the GPU.
+// Lets a test keep one rank's kernel pending at a chosen point while the other ranks run on.
+__global__ void gate_kernel(volatile int* gate, uint64_t timeout_ns) {
+    const uint64_t start = global_timer_ns();
+    while (ld_relaxed_sys(const_cast<const int*>(gate)) == 0) {
+        __nanosleep(500);
+        if (global_timer_ns() - start > timeout_ns) {
+            gate[1] = 1;
+            break;
+        }
+    }
+}
+
 // ---------------------------------------------------------------- wrappers
 #define NEP_KERNEL_PAIR(name, Params, threads)                                                                  \
     __global__ void __launch_bounds__(threads) name##_kernel(const __grid_constant__ Params p) { name##_body(p); } \
@@ -1361,6 +1375,11 @@ cudaError_t launch_combine(const CombineParams* params, LaunchShape shape, size_
     const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
     void* args[1] = {multi ? (void*)&params : (void*)params};
     return cudaLaunchCooperativeKernel(fn, grid, dim3(kCombineThreads), args, smem, stream);
+}
+
+cudaError_t launch_gate(int* gate, uint64_t timeout_ns, cudaStream_t stream) {
+    gate_kernel<<<1, 1, 0, stream>>>(gate, timeout_ns);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream) {

@@ -177,6 +177,8 @@ cudaError_t launch_barrier(const BarrierParams* params, LaunchShape shape, cudaS
 // resident; the block that finishes staging last runs the barrier and releases the others).
 cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullParams* pull, LaunchShape shape, int warps, size_t smem,
                                          cudaStream_t stream);
+// Test utility: one thread that waits (bounded) until gate[0] != 0; gate is pinned host memory that the host writes.
+cudaError_t launch_gate(int* gate, uint64_t timeout_ns, cudaStream_t stream);
 cudaError_t launch_local_combine(const LocalCombineParams* params, LaunchShape shape, cudaStream_t stream);
 
 // Shared-memory plan of the pull/push rings: `warps` independent rings of `stages` row buffers.

@@ -67,6 +67,14 @@ struct CombineTrace {
 };
 CombineTrace g_trace;
 
+// Test hook: while set, every dispatch of this process launches a gate kernel between its planning kernels and its
+// pull, so a test can keep one rank's pull pending (a "slow reader") while its peers run ahead.
+struct TestGate {
+    at::Tensor word;  // pinned host int32[2]: [0] release (written by the host), [1] set by the kernel when its wait ran out
+    double timeout_s = 0;
+};
+TestGate g_gate;
+
 // Single-launch path for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
 // stage, peer barrier and pull as one cooperative launch; `blocks` bounds its grid (every block must be
 // resident at once and spins on one word while the last block runs the peer barrier).  Defaults come from
@@ -427,6 +435,8 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     {
         c10::cuda::CUDAStreamGuard on_comm(s.work);
         const PullParams* dev = upload(pull, keep, cs);
+        if (g_gate.word.defined())
+            cuda_check(launch_gate(g_gate.word.data_ptr<int>(), uint64_t(g_gate.timeout_s * 1e9), cs), "test gate launch");
         g_marks.mark("host_gap", cs);
         PeerWindow::launches += 1;
         int64_t max_items = 1;
@@ -688,6 +698,17 @@ void set_fused_limits(int64_t dispatch_tokens, int64_t blocks) {
 }
 
 void set_phase_timing(bool enabled) { g_marks.enabled = enabled; }
+
+void set_test_gate(const c10::optional<at::Tensor>& word, double timeout_s) {
+    if (!word.has_value()) {
+        g_gate.word = at::Tensor();
+        return;
+    }
+    TORCH_CHECK(word->is_pinned() && word->scalar_type() == at::kInt && word->numel() >= 2 && word->is_contiguous(),
+                "the gate word must be a pinned host int32 tensor with two entries");
+    g_gate.word = *word;
+    g_gate.timeout_s = timeout_s;
+}
 
 void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group) {
     g_trace.enabled = enabled;

@@ -73,6 +73,11 @@ std::vector<double> take_combine_trace();
 // The same for the stage kernel of the last fresh dispatch: microseconds until the routing was counted, the rows
 // were staged, the peer barrier was passed and the tail block finished.
 std::vector<double> take_stage_trace();
+// Test hook: with a pinned host int32[2] tensor set, every dispatch holds its pull behind a kernel that waits (at most
+// `timeout_s`) until the host writes word[0] != 0; word[1] becomes 1 if that wait ran out.  None switches it off.
+// (The word lives in host memory so that opening the gate needs no GPU work: a kernel or copy issued to open it could
+// queue up behind the very kernels the gate holds back.)
+void set_test_gate(const c10::optional<at::Tensor>& word, double timeout_s);
 void set_phase_timing(bool enabled);
 std::vector<std::pair<std::string, double>> take_phase_timings();
 

@@ -4,11 +4,15 @@ Covers what the reference's distributed tier covers through its public API (test
 dispatch_worker.py, arena_worker.py, bootstrap_worker.py): two buffer lifetimes, both layouts, all case
 kinds, bit-exact combine against a source-side rounding model, async + previous_event with delayed
 producers, cached replays with an interleaved foreign dispatch, back-to-back arena reuse, bootstrap
-fault injection with identical aggregated errors, bounded-wait failure detection, misuse errors.
+fault injection with identical aggregated errors, bounded-wait failure detection, misuse errors; a gated slow reader
+whose staged rows must survive peers that run ahead (dispatch_barrier_worker.py:116-158, arena_worker.py:119-139),
+results that outlive newer operations under a slow consumer stream (dispatch_worker.py:161-194), back-to-back
+combines on the single return area, and a synchronous operation followed by a standalone barrier.
 """
 
 import os
 import sys
+import time
 from datetime import timedelta
 from unittest import mock
 
@@ -167,6 +171,135 @@ def lifetime(group, rank, world, multiple):
     return checks
 
 
+def slow_reader_keeps_its_rows(group, rank, world):
+    """Rank 0's pull of dispatch d1 is held behind a gate kernel (a slow reader) while every other rank finishes d1 and
+    queues d2 and d3 (cached, so their hosts do not wait).  d3 reuses d1's staging copy, so it must not start before
+    rank 0 has read it: the staged bytes stay unchanged while the reader is pending, rank 0's result is exact once the
+    gate opens, and afterwards every signal slot holds the epoch of the last operation."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    case = make_case(world, kind="random", seed=41, hidden=256, tokens=23)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, 64)
+    with CudaBuffer(group, cfg, wait_timeout_s=30.0) as buf:
+        x, idx, w = case.xs[rank].cuda(), case.indices[rank].cuda(), case.weights[rank].cuda()
+        first = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=True, alignment=4, zero_padding=True)  # d0, staging copy 0
+        torch.cuda.synchronize()
+        layout = buf.window.layout()
+        rows_d1 = slice(layout["stage_rows_offset"] + layout["stage_rows_stride"],
+                        layout["stage_rows_offset"] + layout["stage_rows_stride"] + x.shape[0] * layout["row_bytes"])
+        gate = torch.zeros(2, dtype=torch.int32).pin_memory()
+        xs1 = [(t.float() * 3).to(torch.bfloat16) for t in case.xs]
+        xs_late = [(t.float() * -5).to(torch.bfloat16) for t in case.xs]
+        x1, late = xs1[rank].cuda(), xs_late[rank].cuda()
+        torch.cuda.synchronize()
+        if rank == 0:
+            ext.set_test_gate(gate, 20.0)
+        try:
+            d1 = buf.dispatch(x1, topk_idx=idx, weights=w, do_expand=True, alignment=4, zero_padding=True, async_op=True)
+        finally:
+            ext.set_test_gate(None)
+        # d2 and d3 replay the routing with other payloads; d3 writes the staging copy that d1 used
+        d2 = buf.dispatch(x, handle=first.handle, weights=w, zero_padding=True, async_op=True)
+        d3 = buf.dispatch(late, handle=first.handle, weights=w, zero_padding=True, async_op=True)
+        time.sleep(0.3)  # let the other ranks' GPUs run as far as they can
+        # While the gate is shut nothing but plain copies is issued on this GPU: a kernel on any stream may be queued by
+        # the hardware behind the kernels the gate holds back, and the host would then wait for the gate's own limit.
+        staged = buf.window.local_window()[rows_d1].cpu()
+        if rank == 0:
+            assert not d1.event.query(), "the gated pull finished early"
+        want = xs1[rank].view(torch.uint8).view(x.shape[0], -1)
+        got_rows = staged.view(x.shape[0], layout["row_bytes"])[:, : 2 * case.hidden]
+        assert torch.equal(got_rows, want), "staged rows changed while a reader was pending"
+        dist.barrier(group=group)
+        gate[0] = 1  # open the gate (only rank 0 ever waits on it); a host store, no GPU work that could queue behind it
+        for pending in (d1, d2, d3):
+            pending.event.current_stream_wait()
+        torch.cuda.synchronize()
+        assert int(gate[1]) == 0, "the gate ran into its own limit"
+        buf.check_status()
+        assert_dispatch_matches(d1, xs1, case.indices, case.weights, case.num_experts, rank, expand=True, alignment=4, zero_padding=True)
+        assert_dispatch_matches(d3, xs_late, case.indices, case.weights, case.num_experts, rank, expand=True, alignment=4, zero_padding=True)
+        signals = buf.window.local_window()[layout["signal_offset"] : layout["signal_offset"] + 8 * world].view(torch.int64).cpu()
+        assert (signals == buf.window.last_epoch).all(), (signals.tolist(), buf.window.last_epoch)
+
+
+def back_to_back_combines(group, rank, world, multiple):
+    """Combines that follow one another without a dispatch in between share the single return area: a rank may only
+    overwrite a peer's partitions once that peer has reduced the previous contents, however the ranks are skewed."""
+    case = make_case(world, kind="random", seed=53, hidden=512, tokens=41)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, 64)
+    with CudaBuffer(group, cfg, allow_multiple_reduction=multiple, wait_timeout_s=30.0) as buf:
+        x, idx, w = case.xs[rank].cuda(), case.indices[rank].cuda(), case.weights[rank].cuda()
+        got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=True, alignment=8, zero_padding=True)
+        outs, wants = [], []
+        for it in range(8):
+            values = choice_values(case, seed=100 + it)
+            y = expert_outputs(values, got, True)
+            if (it + rank) % 2 == 0:
+                torch.cuda._sleep(15_000_000)  # alternate which ranks run late
+            outs.append(buf.combine(y, got.handle).x)
+            wants.append(source_reference(values[rank], case.indices, rank, case.num_experts, world, expand=True,
+                                          allow_multiple_reduction=multiple))
+        torch.cuda.synchronize()
+        buf.check_status()
+        for it, (out, want) in enumerate(zip(outs, wants)):
+            assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16)), f"combine {it} of a back-to-back series is wrong"
+
+
+def results_outlive_newer_operations(group, rank, world):
+    """A slow consumer stream still reads a dispatch result after the caller dropped it and newer dispatches allocated
+    tensors of the same sizes on the communication stream: the completion event registered the result with the
+    consumer stream, so the allocator must not hand its memory out again."""
+    case = make_case(world, kind="random", seed=67, hidden=512, tokens=48)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, 64)
+    with CudaBuffer(group, cfg, wait_timeout_s=30.0) as buf:
+        x, idx, w = case.xs[rank].cuda(), case.indices[rank].cuda(), case.weights[rank].cuda()
+        other = (case.xs[rank].float() * 7).to(torch.bfloat16).cuda()
+        consumer = torch.cuda.Stream()
+        got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=True, alignment=4, zero_padding=True, async_op=True)
+        handle = got.handle
+        with torch.cuda.stream(consumer):
+            got.event.current_stream_wait()
+            torch.cuda._sleep(60_000_000)  # the consumer gets to the result late
+            late_copy = got.x.clone()
+            late_weights = got.topk_weights.clone()
+        del got  # the caller lets go of the result while the consumer stream has not read it yet
+        newer = []
+        for _ in range(4):
+            newer.append(buf.dispatch(other, handle=handle, weights=w, zero_padding=True, async_op=True))
+        for n in newer:
+            n.event.current_stream_wait()
+        torch.cuda.synchronize()
+        buf.check_status()
+        first = buf.dispatch(x, handle=handle, weights=w, zero_padding=True)  # what the first result must have been
+        torch.cuda.synchronize()
+        assert torch.equal(late_copy.view(torch.int16), first.x.view(torch.int16)), "a result was recycled under a slow consumer"
+        assert torch.equal(late_weights, first.topk_weights)
+
+
+def synchronous_operation_then_barrier(group, rank, world):
+    """A synchronous cached dispatch queued behind a long kernel on the caller's stream, then a standalone barrier on the
+    communication stream: the barrier must not overtake the dispatch (its epoch would release the peers early)."""
+    case = make_case(world, kind="random", seed=71, hidden=256, tokens=29)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, 64)
+    with CudaBuffer(group, cfg, wait_timeout_s=30.0) as buf:
+        x, idx, w = case.xs[rank].cuda(), case.indices[rank].cuda(), case.weights[rank].cuda()
+        got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=False)
+        torch.cuda.synchronize()
+        xs2 = [(t.float() * -2).to(torch.bfloat16) for t in case.xs]
+        x2 = xs2[rank].cuda()
+        for it in range(3):
+            if rank % 2 == it % 2:
+                torch.cuda._sleep(30_000_000)  # the caller's stream is busy when the dispatch is queued
+            again = buf.dispatch(x2, handle=got.handle, weights=w)
+            buf.barrier()
+            torch.cuda.synchronize()
+            buf.check_status()
+            assert_dispatch_matches(again, xs2, case.indices, case.weights, case.num_experts, rank, expand=False, alignment=1, zero_padding=False)
+
+
+
 def bootstrap_faults(group, rank, world):
     cfg = EPConfig(2 * world, 2, 256, 8)
     real_load = cuda_buffer._load_native
@@ -264,6 +397,11 @@ def main():
             checks += lifetime(group, rank, world, multiple)
         bootstrap_faults(group, rank, world)
         if world > 1:
+            slow_reader_keeps_its_rows(group, rank, world)
+            results_outlive_newer_operations(group, rank, world)
+            synchronous_operation_then_barrier(group, rank, world)
+            for multiple in (False, True):
+                back_to_back_combines(group, rank, world, multiple)
             missing_peer_is_detected(group, rank, world)
         dist.barrier()
         print(f"NANOEP_RANK_OK={rank} checks={checks}", flush=True)
