@@ -1,10 +1,11 @@
 """Small, self-terminating workloads for kernel profilers (one GPU, a few GB at most).
 
-    python benchmarks/profile_case.py ep      # 2 logical ranks on one GPU: stage, plan, pull, push, reduce (+ single-rank local_combine)
+    python benchmarks/profile_case.py ep      # 2 logical ranks on one GPU: stage, plan, pull, combine (+ single-rank local_combine)
     python benchmarks/profile_case.py gemm    # tcgen05 grouped GEMM: SwiGLU up-projection, down-projection, scatter variant inputs
 
 Inputs are larger than L2 (126 MB) so DRAM figures are meaningful; each kernel of interest runs a
-handful of times.  Meant to be run once plainly and once under ``ncu -k regex:<kernel> -c <n>``.
+handful of times.  Meant to be run once plainly and then once per kernel under
+``ncu --set full --clock-control none -k regex:<one kernel name> -s 1 -c 1`` (one kernel per capture).
 """
 
 import sys
