@@ -61,6 +61,10 @@ def parse_args():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-nccl-anchor", action="store_true", help="skip the NCCL arm that fills vs_baseline")
     p.add_argument("--detail", action="store_true", help="record per-kernel device times (median, max over ranks) in phases_us")
+    p.add_argument("--trace", action="store_true",
+                   help="after the timed steps, run a few more with the kernels' own %%globaltimer stamps switched on and report them per rank "
+                        "in kernel_trace_us (combine: transfer warps done, flags published, reduce warps done; stage: routing counted, rows "
+                        "staged, peer barrier passed, tail done; microseconds from the kernel's first block)")
     return p.parse_args()
 
 
@@ -412,6 +416,25 @@ def run_ours(args, rank, world, device, control_group):
         # gathered routing, every dispatched row against its source token, the round trip bit for bit
         verified, verify_note = verify_round_trip(args, buf, rank, world, device, control_group, x, idx, w, expand)
 
+        kernel_trace = None
+        if args.trace:
+            ext.set_combine_trace(True, 0, 0)
+            seen = {"combine": [], "stage": []}
+            for i in range(12):
+                step(x_sets[i % len(x_sets)], idx, w)
+                torch.cuda.synchronize()
+                combine_stamps, stage_stamps = ext.take_combine_trace(), ext.take_stage_trace()
+                if i >= 3:
+                    seen["combine"].append(combine_stamps)
+                    seen["stage"].append(stage_stamps)
+                dist.barrier(group=control_group)
+            ext.set_combine_trace(False, 0, 0)
+            mine = {k: [round(statistics.median(r[j] for r in rows), 1) for j in range(len(rows[0]))] if rows and rows[0] else []
+                    for k, rows in seen.items()}
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine, group=control_group)
+            kernel_trace = {k: [g[k] for g in gathered] for k in ("combine", "stage")}
+
         # ---- end to end through the public API: every step copies its inputs from pinned host memory (on a copy
         # stream, one step ahead) and reads its result back into pinned host memory (on a second copy stream,
         # overlapping the next step); the host touches each result once it is there.  Two passes: the headline reads
@@ -559,6 +582,7 @@ def run_ours(args, rank, world, device, control_group):
         "wall_ms_per_step": max_over_ranks(wall * 1e3) / args.steps,
         "gpu_launches": launches,
         "phases_us": phases,
+        "kernel_trace_us": kernel_trace,
         "clocks": clock_summary,
         "e2e": e2e,
     }
