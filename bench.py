@@ -14,7 +14,9 @@ receives N deduplicated rows in dispatch and C_valid assignment rows come back i
 (sum over ranks of N + C_valid) * hidden * 2, divided by the slowest rank's device time per step.
 
 Arms: ``--impl ours`` (default), ``--impl nccl`` (torch.distributed all_to_all_single + index ops, a
-baseline), ``--impl reference`` (the reference package; not installable offline, prints why).
+baseline), ``--impl reference`` (the reference package; not installable offline, prints why), ``--impl refkernels``
+(context only: the reference's own code with its JIT replaced by ahead-of-time instantiations, built by
+``python baseline/refkernels/build.py``; labelled as such in its JSON line).
 
 After the timed steps the ``ours`` arm checks, untimed, what it has just timed: receive counts against a count
 of the all-gathered routing, every dispatched row against its source token, and the round trip bit for bit.
@@ -47,7 +49,7 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=5)
-    p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
+    p.add_argument("--impl", choices=("ours", "nccl", "reference", "refkernels"), default="ours")
     p.add_argument("--tokens", type=int, default=4096)
     p.add_argument("--hidden", type=int, default=7168)
     p.add_argument("--experts", type=int, default=256)
@@ -691,6 +693,86 @@ def run_nccl(args, rank, world, device, control_group, sample_clocks=True):
     }
 
 
+def run_refkernels(args, rank, world, device, control_group):
+    """Context only, NOT the reference arm: the reference's own Python package, host runtime and kernel templates,
+    with its run-time JIT (which cannot be built offline) replaced by ahead-of-time instantiations
+    (baseline/refkernels).  Same inputs, same timing and the same round-trip check as the ``ours`` arm."""
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "refkernels"))
+    import build as refbuild
+
+    nano_ep = refbuild.reference_package()
+    cfg = nano_ep.EPConfig(args.experts, args.topk, args.hidden, args.tokens)
+    hx, hidx, hw = make_inputs(args, rank, world, device)
+    x, idx, w = hx.to(device), hidx.to(device), hw.to(device)
+    copies = max(2, -(-(192 << 20) // max(1, x.numel() * 2)))
+    x_sets = [x] + [x.clone() for _ in range(copies - 1)]
+
+    def reduce_max(value):
+        t = torch.tensor([value], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=control_group)
+        return float(t.item())
+
+    with nano_ep.CudaBuffer(control_group, cfg) as buf:
+        def step(xd):
+            got = buf.dispatch(xd, topk_idx=idx, weights=w, do_expand=True, alignment=args.alignment, zero_padding=True)
+            return got, buf.combine(got.x, got.handle)
+
+        for _ in range(args.warmup):
+            got, back = step(x)
+        torch.cuda.synchronize()
+        dist.barrier(group=control_group)
+        n_rows = got.handle.layout.recv_count
+        c_valid = int(got.handle.layout.expert_counts.sum().item())
+        starts, mids, ends = ([torch.cuda.Event(enable_timing=True) for _ in range(args.steps)] for _ in range(3))
+        gc.collect()
+        gc.disable()
+        for i in range(args.steps):
+            xi = x_sets[i % len(x_sets)]
+            starts[i].record()
+            got = buf.dispatch(xi, topk_idx=idx, weights=w, do_expand=True, alignment=args.alignment, zero_padding=True)
+            mids[i].record()
+            back = buf.combine(got.x, got.handle)
+            ends[i].record()
+        torch.cuda.synchronize()
+        dist.barrier(group=control_group)
+        gc.enable()
+        step_ms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
+        ms_per_step = reduce_max(sum(step_ms)) / args.steps
+        disp_us = reduce_max(statistics.median(a.elapsed_time(b) for a, b in zip(starts, mids))) * 1e3
+        comb_us = reduce_max(statistics.median(a.elapsed_time(b) for a, b in zip(mids, ends))) * 1e3
+        # the same identity-expert check as the ours arm: token times the number of rows that came back, rounded once
+        got, back = step(x)
+        torch.cuda.synchronize()
+        count = (idx >= 0).sum(-1, keepdim=True).float()
+        want = (x.float() * count).to(x.dtype)
+        ok = bool(torch.equal(back.x.view(torch.int16), want.view(torch.int16)))
+        flags = [None] * world
+        dist.all_gather_object(flags, ok, group=control_group)
+        rows = torch.tensor([float(n_rows + c_valid)], dtype=torch.float64)
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=control_group)
+    bytes_per_step = float(rows.item()) * args.hidden * 2
+    ordered = sorted(step_ms)
+    return {
+        "metric": "ep_dispatch_combine_payload_GBps", "value": bytes_per_step / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (same generator and seeds as the ours arm)",
+        "impl": "reference kernels, AOT stand-in, not the stock build",
+        "what": "the reference's unmodified Python package, host runtime (peer.cu, pipeline.cu, epilogue wrappers, bindings) and kernel "
+                "templates compiled for sm_100a; only its run-time JIT glue (csrc/jit.cpp) is replaced by static instantiations",
+        "edits_to_reference_sources": "peer.cu:114-125 (owner lookup of mapped peer pointers and the three checks on it) removed: the lookup "
+                                      "names the importing GPU on this driver and stops every multi-GPU run"
+        if os.path.exists(os.path.join(str(refbuild.REF_OUT), "PEER_CHECKS_REMOVED")) else "none",
+        "dispatch_us": disp_us, "combine_us": comb_us, "verified": all(flags),
+        "step_ms_percentiles": {"p10": reduce_max(ordered[int(0.1 * len(ordered))]), "p50": reduce_max(ordered[len(ordered) // 2]),
+                                "p90": reduce_max(ordered[min(len(ordered) - 1, int(0.9 * len(ordered)))])},
+        "config": {"tokens_per_rank": args.tokens, "hidden": args.hidden, "experts": args.experts, "topk": args.topk,
+                   "layout": "expanded", "alignment": args.alignment, "zero_padding": True, "parallelism": f"ep{world}"},
+    }
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -721,7 +803,7 @@ def main():
     dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, timeout=timedelta(seconds=300), device_id=device)
     try:
         control = dist.new_group(backend="gloo", timeout=timedelta(seconds=300))
-        runner = run_ours if args.impl == "ours" else run_nccl
+        runner = {"ours": run_ours, "nccl": run_nccl, "refkernels": run_refkernels}[args.impl]
         line = runner(args, rank, world, device, control)
         if rank == 0:
             print(json.dumps(line), flush=True)
