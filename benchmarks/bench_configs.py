@@ -36,6 +36,8 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", choices=("ours", "nccl"), default="ours")
     p.add_argument("--tokens", type=str, default="1,8,32,128,512,4096")
+    p.add_argument("--per-size-buffers", action="store_true",
+                   help="decode: a buffer per token count (num_max_tokens_per_rank = tokens) instead of one sized for the largest")
     p.add_argument("--fused", type=str, default="",
                    help="decode/published: comma-separated dispatch_tokens:blocks settings of the single-launch cached dispatch to "
                         "measure one after the other (empty: the library defaults)")
@@ -124,8 +126,13 @@ def main():
 
             ext = load_extension()
             settings = [tuple(int(v) for v in item.split(":")) for item in args.fused.split(",") if item] or [ext.fused_limits()]
-            with CudaBuffer(control, EPConfig(E, K, H, max(sizes))) as buf:
-                for setting, T in ((s_, t_) for s_ in settings for t_ in sizes):
+            # one buffer for all sizes, or (--per-size-buffers) one per size with num_max_tokens_per_rank = that size, as a
+            # server with a small maximum batch would configure it: the single-launch fresh dispatch sizes its outputs by
+            # that maximum and is only used when the bound is modest
+            groups = [[t] for t in sizes] if args.per_size_buffers else [sizes]
+            for group_sizes in groups:
+              with CudaBuffer(control, EPConfig(E, K, H, max(group_sizes))) as buf:
+                for setting, T in ((s_, t_) for s_ in settings for t_ in group_sizes):
                     ext.set_fused_limits(*setting)
                     idx, w = uniform_routing(T, E, K, seed=3 + rank)
                     x = torch.randn(T, H, generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16).to(device)
@@ -181,6 +188,7 @@ def main():
                             host_comb.append((h3 - h2) * 1e3)
                     buf.check_status()
                     rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H,
+                           "buffer_max_tokens": max(group_sizes),
                            "single_launch_limits": dict(zip(("dispatch_tokens", "blocks"), ext.fused_limits()))}
                     if args.config == "published":
                         # reference figure (single-node H20): NanoEP / DeepEP 2.1.0 microseconds

@@ -39,21 +39,21 @@ __device__ __forceinline__ bool take_last_ticket(int* ticket) {
 // blocks of its rank the outcome through one word: +tag = go, -tag = failed (tag derives from the epoch, never 0).
 __device__ __forceinline__ int go_tag(uint64_t epoch) { return int(epoch & 0x3fffffff) | 0x40000000; }
 
-__device__ __forceinline__ void publish_go(int* ctrl, uint64_t epoch, bool ok) {
+__device__ __forceinline__ void publish_go(int* ctrl, uint64_t epoch, bool ok, int word = WindowLayout::kGoWord) {
     const int want = go_tag(epoch);
     __threadfence();
-    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctrl + WindowLayout::kGoWord), "r"(ok ? want : -want) : "memory");
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctrl + word), "r"(ok ? want : -want) : "memory");
 }
 
 // Called by every thread of a block; thread 0 polls (bounded), the block gets the outcome.
-__device__ bool wait_go(int* ctrl, uint64_t epoch, uint64_t timeout_ns, StatusRef status, uint32_t tag) {
+__device__ bool wait_go(int* ctrl, uint64_t epoch, uint64_t timeout_ns, StatusRef status, uint32_t tag, int word = WindowLayout::kGoWord) {
     __shared__ int s_go;
     if (threadIdx.x == 0) {
         const int want = go_tag(epoch);
         const uint64_t start = global_timer_ns();
         int seen = 0;
         for (;;) {
-            seen = ld_acquire_gpu(ctrl + WindowLayout::kGoWord);
+            seen = ld_acquire_gpu(ctrl + word);
             if (seen == want || seen == -want) break;
             __nanosleep(32);
             if (global_timer_ns() - start > 2 * timeout_ns) {
@@ -178,7 +178,11 @@ __device__ bool stage_body(const StageParams& p) {
             if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, R, L.data_signal_offset, p.epoch);
         }
         stamp(2);
-        if (!runs_tail) return false;
+        if (!runs_tail) {
+            // single-launch fresh dispatch: wait for the tail block's prefixes before planning
+            if (!p.fused) return false;
+            return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
+        }
     } else if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
         if (!p.fused) return false;
         return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
@@ -217,7 +221,7 @@ __device__ bool stage_body(const StageParams& p) {
     }
     __syncthreads();
     stamp(3);
-    if (p.fused) {
+    if (p.fused && !p.fresh) {
         if (tid == 0) publish_go(ctrl, p.epoch, s_ok != 0);
         return s_ok != 0;
     }
@@ -227,6 +231,7 @@ __device__ bool stage_body(const StageParams& p) {
             p.mailbox[1] = -2;
             p.mailbox[0] = -2;
             __threadfence_system();
+            if (p.fused) publish_go(ctrl, p.epoch, false);
         }
         return false;
     }
@@ -302,6 +307,7 @@ __device__ bool stage_body(const StageParams& p) {
         p.mailbox[1] = s_total[1];
         p.mailbox[0] = s_total[0];
         __threadfence_system();
+        if (p.fused) publish_go(ctrl, p.epoch, true);  // the other blocks of a single-launch dispatch go on to plan
     }
     stamp(4);
     return true;
@@ -1246,6 +1252,34 @@ NEP_KERNEL_PAIR(reduce, ReduceParams, kReduceThreads)
 NEP_KERNEL_PAIR(barrier, BarrierParams, 32)
 NEP_KERNEL_PAIR(local_combine, LocalCombineParams, kReduceThreads)
 
+// Fresh dispatch of a small call in ONE cooperative launch: stage (count exchange, peer barrier, prefixes, mailbox),
+// plan, pull.  Outputs are sized by the caller at an upper bound and trimmed on the host once N and C are known, so
+// the host's wait for the mailbox runs beside the kernel instead of between two launches.
+__device__ void fused_fresh_dispatch_body(const StageParams& sp, const PlanParams& lp, const PullParams& pp) {
+    if (!stage_body(sp)) return;
+    plan_body(lp);
+    // every block of this rank has planned its chunks before any row is pulled
+    int* ctrl = ctrl_words(sp.c);
+    if (take_last_ticket(ctrl + WindowLayout::kTicketPlan)) {
+        if (threadIdx.x == 0) {
+            ctrl[WindowLayout::kTicketPlan] = 0;
+            publish_go(ctrl, sp.epoch, true, WindowLayout::kGoWordPlan);
+        }
+    } else if (!wait_go(ctrl, sp.epoch, sp.c.timeout_ns, status_of(sp.c), kTagPlan, WindowLayout::kGoWordPlan)) {
+        return;
+    }
+    __syncthreads();
+    fence_proxy_async();
+    pull_body(pp);
+}
+__global__ void __launch_bounds__(256) fused_fresh_dispatch_kernel(const __grid_constant__ StageParams sp, const __grid_constant__ PlanParams lp,
+                                                                   const __grid_constant__ PullParams pp) {
+    fused_fresh_dispatch_body(sp, lp, pp);
+}
+__global__ void __launch_bounds__(256) fused_fresh_dispatch_multi_kernel(const StageParams* sp, const PlanParams* lp, const PullParams* pp) {
+    fused_fresh_dispatch_body(sp[blockIdx.y], lp[blockIdx.y], pp[blockIdx.y]);
+}
+
 // stage + peer barrier + pull in one cooperative launch (cached dispatch, small calls)
 __global__ void __launch_bounds__(256) fused_cached_dispatch_kernel(const __grid_constant__ StageParams sp, const __grid_constant__ PullParams pp) {
     if (!stage_body(sp)) return;
@@ -1357,6 +1391,27 @@ cudaError_t launch_fused_cached_dispatch(const StageParams* stage, const PullPar
                               warps, smem, stream, granted);
 }
 
+cudaError_t launch_fused_fresh_dispatch(const StageParams* stage, const PlanParams* plan, const PullParams* pull, LaunchShape shape, int warps,
+                                        size_t smem, cudaStream_t stream) {
+    const bool multi = shape.ranks_y > 1;
+    const void* fn = multi ? (const void*)fused_fresh_dispatch_multi_kernel : (const void*)fused_fresh_dispatch_kernel;
+    static thread_local size_t granted[2][64] = {};
+    if (smem > 48 * 1024) {
+        int device = 0;
+        cudaGetDevice(&device);
+        size_t& have = granted[multi ? 1 : 0][device & 63];
+        if (smem > have) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return e;
+            have = smem;
+        }
+    }
+    const dim3 grid(shape.grid_x, multi ? shape.ranks_y : 1);
+    void* args_multi[3] = {(void*)&stage, (void*)&plan, (void*)&pull};
+    void* args_single[3] = {(void*)stage, (void*)plan, (void*)pull};
+    return cudaLaunchCooperativeKernel(fn, grid, dim3(warps * 32), multi ? args_multi : args_single, smem, stream);
+}
+
 cudaError_t launch_combine(const CombineParams* params, LaunchShape shape, size_t smem, cudaStream_t stream, bool cooperative) {
     if (!cooperative) return launch_pair<CombineParams>(combine_kernel, combine_multi_kernel, params, shape, kCombineThreads, smem, stream);
     const bool multi = shape.ranks_y > 1;
@@ -1395,6 +1450,7 @@ int kernel_table(KernelInfo* out, int capacity) {
         {"stage", (const void*)stage_kernel},   {"plan", (const void*)plan_kernel},     {"pull", (const void*)pull_kernel},
         {"combine", (const void*)combine_kernel}, {"reduce", (const void*)reduce_kernel}, {"barrier", (const void*)barrier_kernel},
         {"local_combine", (const void*)local_combine_kernel}, {"fused_cached_dispatch", (const void*)fused_cached_dispatch_kernel},
+        {"fused_fresh_dispatch", (const void*)fused_fresh_dispatch_kernel},
     };
     int n = 0;
     for (const Entry& e : entries) {

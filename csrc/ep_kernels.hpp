@@ -169,6 +169,9 @@ struct LaunchShape {
 cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
 cudaError_t launch_plan(const PlanParams* params, LaunchShape shape, size_t smem, cudaStream_t stream);
 cudaError_t launch_pull(const PullParams* params, LaunchShape shape, int warps, size_t smem, cudaStream_t stream);
+// Fresh dispatch for small calls: stage, plan and pull in ONE cooperative launch; outputs sized at an upper bound.
+cudaError_t launch_fused_fresh_dispatch(const StageParams* stage, const PlanParams* plan, const PullParams* pull, LaunchShape shape, int warps,
+                                        size_t smem, cudaStream_t stream);
 // `cooperative`: every block must be resident at once (a whole logical group in one launch waits on itself).
 cudaError_t launch_combine(const CombineParams* params, LaunchShape shape, size_t smem, cudaStream_t stream, bool cooperative);
 cudaError_t launch_reduce(const ReduceParams* params, LaunchShape shape, cudaStream_t stream);

@@ -26,6 +26,7 @@ namespace nep {
 namespace {
 
 constexpr int kFusedDispatchDefaultTokens = 64;
+constexpr int64_t kFusedFreshMaxOutputBytes = int64_t(256) << 20;  // single-launch fresh dispatch: largest bound-sized output
 constexpr int kFusedDefaultBlocks = 1024;  // i.e. bounded by the SM budget and co-residency only
 
 void cuda_check(cudaError_t e, const char* what) {
@@ -337,17 +338,29 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     bool gated = false;
     for (const auto& t : tile_ready) gated = gated || t.has_value();
     const bool fuse_small = !fresh && !gated && max_tokens_now <= fused_dispatch_max_tokens();
+    // Small fresh calls: stage, plan and pull as ONE cooperative launch writing into outputs sized at an upper bound
+    // (every rank may send all of its Tmax tokens here), trimmed to N / C once the mailbox has them.  Only when that
+    // bound is modest, i.e. for buffers configured for small batches.
+    const int64_t bound_rows_n = int64_t(L.ranks) * L.max_tokens;
+    const int64_t bound_rows_c = bound_rows_n * std::min<int64_t>(L.topk, L.local_experts) + int64_t(L.local_experts) * (alignment - 1);
+    const int64_t bound_bytes = (expand ? bound_rows_c : bound_rows_n) * L.hidden * 2;
+    const bool fuse_fresh = fresh && !gated && !g_gate.word.defined() && max_tokens_now <= fused_dispatch_max_tokens() &&
+                            bound_bytes <= kFusedFreshMaxOutputBytes && (!expand || bound_rows_c <= L.slot_scratch_ints) &&
+                            ring.warps >= 2 && ring.smem_bytes >= size_t(stage_smem_bytes(L)) &&
+                            ring.smem_bytes >= size_t(ring.warps) * 32 * L.topk * 4;
     const StageParams* stage_dev = nullptr;
+    const PlanParams* plan_dev = nullptr;
+    std::vector<PlanParams> plan(fresh ? n : 0);  // outlives the launches: a single-rank call passes it by host pointer
     {
         c10::cuda::CUDAStreamGuard on_comm(s.work);
-        for (int i = 0; i < n; ++i) stage[i].fused = fuse_small ? 1 : 0;
+        for (int i = 0; i < n; ++i) stage[i].fused = (fuse_small || fuse_fresh) ? 1 : 0;
         stage_dev = upload(stage, keep, cs);
         if (fresh && g_trace.enabled && n == 1) {
             const int64_t init[5] = {INT64_MAX, 0, 0, 0, 0};
             cuda_check(cudaMemcpyAsync(g_trace.stage_words.data_ptr(), init, sizeof(init), cudaMemcpyHostToDevice, cs), "trace reset");
         }
         g_marks.mark("begin", cs);
-        if (!fuse_small) {
+        if (!fuse_small && !fuse_fresh) {
             PeerWindow::launches += 1;
             // 16 warps per block, 4 row quarters per token: small calls get small grids
             const int stage_grid = int(std::max<int64_t>(1, std::min<int64_t>(2 * num_sms, (max_tokens_now * 4 + 15) / 16)));
@@ -355,7 +368,6 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             g_marks.mark("stage", cs);
         }
         if (fresh) {
-            std::vector<PlanParams> plan(n);
             for (int i = 0; i < n; ++i) {
                 plan[i].c = stage[i].c;
                 plan[i].parity = parity[i];
@@ -363,14 +375,18 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             }
             const int chunks = L.ranks * int((L.max_tokens + 31) / 32);
             const int grid = std::max(1, std::min((chunks + 7) / 8, 4 * lim.sms));
-            const PlanParams* pdev = upload(plan, keep, cs);
-            PeerWindow::launches += 1;
-            cuda_check(launch_plan(pdev, LaunchShape{grid, n}, size_t(plan_smem_bytes(L)), cs), "plan launch");
-            g_marks.mark("plan", cs);
+            plan_dev = upload(plan, keep, cs);
+            if (!fuse_fresh) {
+                PeerWindow::launches += 1;
+                cuda_check(launch_plan(plan_dev, LaunchShape{grid, n}, size_t(plan_smem_bytes(L)), cs), "plan launch");
+                g_marks.mark("plan", cs);
+            }
         }
     }
     for (int i = 0; i < n; ++i) {
-        if (fresh) {
+        if (fuse_fresh) {
+            out.counts[i] = {bound_rows_n, expand ? bound_rows_c : 0};  // allocation sizes; the real counts follow the launch
+        } else if (fresh) {
             std::pair<int64_t, int64_t> nc;
             {
                 pybind11::gil_scoped_release release;
@@ -442,7 +458,15 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         int64_t max_items = 1;
         for (int i = 0; i < n; ++i) max_items = std::max<int64_t>(max_items, expand ? out.counts[i].second : out.counts[i].first * L.ranks);
         const int pull_grid = int(std::max<int64_t>(1, std::min<int64_t>(num_sms, (max_items + ring.warps - 1) / ring.warps)));
-        if (fuse_small) {
+        if (fuse_fresh) {
+            const int64_t work = std::max<int64_t>(max_tokens_now * int64_t(L.ranks) * (expand ? std::min<int64_t>(L.topk, L.local_experts) : 1),
+                                                   max_tokens_now * 4);
+            const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), fused_max_blocks(),
+                                                                               (work + ring.warps - 1) / ring.warps})));
+            cuda_check(launch_fused_fresh_dispatch(stage_dev, plan_dev, dev, LaunchShape{fused_grid, n}, ring.warps, ring.smem_bytes, cs),
+                       "fused fresh dispatch launch");
+            g_marks.mark("fused_fresh_dispatch", cs);
+        } else if (fuse_small) {
             // every block must be resident at once (one block per SM with this ring): bound the grid
             const int64_t work = std::max<int64_t>(max_items, max_tokens_now * 4);
             const int fused_grid = int(std::max<int64_t>(1, std::min<int64_t>({int64_t(num_sms), int64_t(lim.sms / n), fused_max_blocks(),
@@ -453,6 +477,27 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
         } else {
             cuda_check(launch_pull(dev, LaunchShape{pull_grid, n}, ring.warps, ring.smem_bytes, cs), "pull launch");
             g_marks.mark("pull", cs);
+        }
+    }
+    if (fuse_fresh) {
+        // The kernel is on its way; now wait for N and C and trim the outputs to their exact sizes (leading-dimension
+        // views of the bound-sized allocations: contiguous, same storage).
+        for (int i = 0; i < n; ++i) {
+            std::pair<int64_t, int64_t> nc;
+            {
+                pybind11::gil_scoped_release release;
+                nc = wins[i]->wait_mailbox(cs, mailbox_timeout_s);
+            }
+            const int64_t N = nc.first, C = nc.second;
+            TORCH_CHECK(N <= bound_rows_n && (!expand || C <= bound_rows_c), "receive counts exceed the single-launch bound");
+            out.counts[i] = {N, C};
+            auto& m = out.metadata[i];
+            auto& o = out.outputs[i];
+            m[0] = m[0].narrow(0, 0, N);
+            if (expand) m[7] = m[7].narrow(0, 0, C);
+            o[0] = o[0].narrow(0, 0, expand ? C : N);
+            if (!expand) o[1] = o[1].narrow(0, 0, N);
+            if (weighted) o[2] = o[2].narrow(0, 0, expand ? C : N);
         }
     }
     std::vector<at::Tensor> inputs, results;
