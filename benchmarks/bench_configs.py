@@ -39,7 +39,7 @@ def parse_args():
     p.add_argument("--per-size-buffers", action="store_true",
                    help="decode: a buffer per token count (num_max_tokens_per_rank = tokens) instead of one sized for the largest")
     p.add_argument("--fused", type=str, default="",
-                   help="decode/published: comma-separated dispatch_tokens:blocks settings of the single-launch cached dispatch to "
+                   help="decode/published: comma-separated dispatch_tokens:blocks[:fresh_tokens] settings of the single-launch dispatch paths to "
                         "measure one after the other (empty: the library defaults)")
     return p.parse_args()
 
@@ -189,7 +189,7 @@ def main():
                     buf.check_status()
                     rec = {"bench": args.config, "impl": "ours", "n_gpus": world, "tokens_per_rank": T, "hidden": H,
                            "buffer_max_tokens": max(group_sizes),
-                           "single_launch_limits": dict(zip(("dispatch_tokens", "blocks"), ext.fused_limits()))}
+                           "single_launch_limits": dict(zip(("dispatch_tokens", "blocks", "fresh_tokens"), ext.fused_limits()))}
                     if args.config == "published":
                         # reference figure (single-node H20): NanoEP / DeepEP 2.1.0 microseconds
                         published = {2: (69.4, 40.2, 51.9), 4: (78.5, 54.9, 70.4), 8: (147.1, 91.8, 102.5)}.get(world)

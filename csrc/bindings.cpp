@@ -170,9 +170,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("group_barrier", &nep::group_barrier);
     m.def("fused_limits", [] {
         const nep::FusedLimits f = nep::fused_limits();
-        return py::make_tuple(f.dispatch_tokens, f.blocks);
+        return py::make_tuple(f.dispatch_tokens, f.blocks, f.fresh_tokens);
     });
-    m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1);
+    m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1, py::arg("fresh_tokens") = -1);
     m.def("set_test_gate", &nep::set_test_gate, py::arg("word"), py::arg("timeout_s") = 10.0);
     m.def("set_phase_timing", &nep::set_phase_timing);
     m.def("set_combine_trace", &nep::set_combine_trace, py::arg("enabled"), py::arg("store_depth") = 0, py::arg("reduce_group") = 0);

@@ -26,6 +26,7 @@ namespace nep {
 namespace {
 
 constexpr int kFusedDispatchDefaultTokens = 64;
+constexpr int kFusedFreshDefaultTokens = 0;  // single-launch fresh dispatch: off unless asked for (see DESIGN.md for the measurement)
 constexpr int64_t kFusedFreshMaxOutputBytes = int64_t(256) << 20;  // single-launch fresh dispatch: largest bound-sized output
 constexpr int kFusedDefaultBlocks = 1024;  // i.e. bounded by the SM budget and co-residency only
 
@@ -76,13 +77,14 @@ struct TestGate {
 };
 TestGate g_gate;
 
-// Single-launch path for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
-// stage, peer barrier and pull as one cooperative launch; `blocks` bounds its grid (every block must be
+// Single-launch paths for small calls.  Cached dispatches of at most `dispatch_tokens` tokens per rank run
+// stage, peer barrier and pull as one cooperative launch; fresh dispatches of at most `fresh_tokens` tokens run
+// stage, plan and pull as one (NANOEP_FUSED_FRESH_TOKENS, default 0 = off); `blocks` bounds their grids (every block must be
 // resident at once and spins on one word while the last block runs the peer barrier).  Defaults come from
 // NANOEP_FUSED_DISPATCH_TOKENS / NANOEP_FUSED_BLOCKS (0 tokens switches the path off) and can be changed
 // at run time.  (A combine is one launch at every size.)
 struct FusedLimitsState {
-    std::atomic<int64_t> dispatch_tokens, blocks;
+    std::atomic<int64_t> dispatch_tokens, blocks, fresh_tokens;
     FusedLimitsState() {
         auto read = [](const char* name, int64_t fallback) {
             const char* env = std::getenv(name);
@@ -90,6 +92,7 @@ struct FusedLimitsState {
         };
         dispatch_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_DISPATCH_TOKENS", kFusedDispatchDefaultTokens));
         blocks = std::max<int64_t>(1, read("NANOEP_FUSED_BLOCKS", kFusedDefaultBlocks));
+        fresh_tokens = std::max<int64_t>(0, read("NANOEP_FUSED_FRESH_TOKENS", kFusedFreshDefaultTokens));
     }
 };
 FusedLimitsState& fused_state() {
@@ -97,6 +100,7 @@ FusedLimitsState& fused_state() {
     return state;
 }
 int64_t fused_dispatch_max_tokens() { return fused_state().dispatch_tokens.load(std::memory_order_relaxed); }
+int64_t fused_fresh_max_tokens() { return fused_state().fresh_tokens.load(std::memory_order_relaxed); }
 int64_t fused_max_blocks() { return fused_state().blocks.load(std::memory_order_relaxed); }
 
 struct DeviceLimits {
@@ -344,7 +348,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
     const int64_t bound_rows_n = int64_t(L.ranks) * L.max_tokens;
     const int64_t bound_rows_c = bound_rows_n * std::min<int64_t>(L.topk, L.local_experts) + int64_t(L.local_experts) * (alignment - 1);
     const int64_t bound_bytes = (expand ? bound_rows_c : bound_rows_n) * L.hidden * 2;
-    const bool fuse_fresh = fresh && !gated && !g_gate.word.defined() && max_tokens_now <= fused_dispatch_max_tokens() &&
+    const bool fuse_fresh = fresh && !gated && !g_gate.word.defined() && max_tokens_now <= fused_fresh_max_tokens() &&
                             bound_bytes <= kFusedFreshMaxOutputBytes && (!expand || bound_rows_c <= L.slot_scratch_ints) &&
                             ring.warps >= 2 && ring.smem_bytes >= size_t(stage_smem_bytes(L)) &&
                             ring.smem_bytes >= size_t(ring.warps) * 32 * L.topk * 4;
@@ -735,10 +739,11 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
     return outs;
 }
 
-FusedLimits fused_limits() { return FusedLimits{fused_dispatch_max_tokens(), fused_max_blocks()}; }
+FusedLimits fused_limits() { return FusedLimits{fused_dispatch_max_tokens(), fused_max_blocks(), fused_fresh_max_tokens()}; }
 
-void set_fused_limits(int64_t dispatch_tokens, int64_t blocks) {
+void set_fused_limits(int64_t dispatch_tokens, int64_t blocks, int64_t fresh_tokens) {
     if (dispatch_tokens >= 0) fused_state().dispatch_tokens = dispatch_tokens;
+    if (fresh_tokens >= 0) fused_state().fresh_tokens = fresh_tokens;
     if (blocks >= 1) fused_state().blocks = blocks;
 }
 

@@ -58,11 +58,11 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
 // Per-phase device times (name, microseconds) of the operations issued since the last call.
 // Token threshold and grid bound of the single-launch cached dispatch for small calls (see pipeline.cpp).
 struct FusedLimits {
-    int64_t dispatch_tokens, blocks;
+    int64_t dispatch_tokens, blocks, fresh_tokens;
 };
 FusedLimits fused_limits();
 // Negative token values / blocks < 1 leave the respective setting unchanged.
-void set_fused_limits(int64_t dispatch_tokens, int64_t blocks);
+void set_fused_limits(int64_t dispatch_tokens, int64_t blocks, int64_t fresh_tokens);
 
 // In-kernel time stamps of the next combines of this process (single-rank calls): microseconds from the
 // kernel's first block to the end of its transfer warps, its flag publishers and its reduce warps.

@@ -114,7 +114,7 @@ def lifetime(group, rank, world, multiple):
         before = ext.fused_limits()
         try:
             for limit in (1 << 20, 0):
-                ext.set_fused_limits(dispatch_tokens=limit)
+                ext.set_fused_limits(dispatch_tokens=limit, fresh_tokens=limit)
                 for kind in ("random", "masked"):
                     case = make_case(world, kind=kind, seed=31, hidden=512, tokens=37)
                     for expand in (False, True):

@@ -22,9 +22,9 @@ def launch_path(request):
     ext = load_extension()
     before = ext.fused_limits()
     if request.param == "single_launch":
-        ext.set_fused_limits(dispatch_tokens=1 << 20)
+        ext.set_fused_limits(dispatch_tokens=1 << 20, fresh_tokens=1 << 20)
     else:
-        ext.set_fused_limits(dispatch_tokens=0)
+        ext.set_fused_limits(dispatch_tokens=0, fresh_tokens=0)
     yield request.param
     ext.set_fused_limits(*before)
 
