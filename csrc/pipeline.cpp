@@ -297,13 +297,22 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             const int64_t T = xs[i].size(0);
             auto& m = out.metadata[i];
             if (fresh) {
+                // one allocation, six views: allocator calls sit on the host's critical path of a small fresh dispatch
                 m.resize(8);
-                m[1] = at::empty({L.local_experts}, i64);
-                m[2] = at::empty({L.local_experts + 1}, i64);
-                m[3] = at::empty({T, L.ranks}, i64);
-                m[4] = at::empty({L.ranks}, i64);
-                m[5] = at::empty({T, L.topk}, i64);
-                m[6] = at::empty({L.ranks}, i64);
+                const int64_t Le = L.local_experts, R = L.ranks, K = L.topk;
+                at::Tensor block = at::empty({Le + (Le + 1) + T * R + R + T * K + R}, i64);
+                int64_t at_ = 0;
+                auto take = [&](int64_t count) {
+                    at::Tensor view = block.narrow(0, at_, count);
+                    at_ += count;
+                    return view;
+                };
+                m[1] = take(Le);
+                m[2] = take(Le + 1);
+                m[3] = take(T * R).view({T, R});
+                m[4] = take(R);
+                m[5] = take(T * K).view({T, K});
+                m[6] = take(R);
             } else {
                 m = cached_meta[i];
             }
@@ -408,8 +417,10 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             const int64_t N = out.counts[i].first, C = out.counts[i].second;
             auto& m = out.metadata[i];
             if (fresh) {
-                m[0] = at::empty({N, L.topk + 2}, i32);
-                m[7] = at::empty({expand ? C : 0}, i32);
+                const int64_t cells = N * (L.topk + 2), slots = expand ? C : 0;
+                at::Tensor block = at::empty({cells + slots}, i32);
+                m[0] = block.narrow(0, 0, cells).view({N, L.topk + 2});
+                m[7] = block.narrow(0, cells, slots);
             }
             auto& o = out.outputs[i];
             o.resize(3);
