@@ -257,7 +257,6 @@ __device__ bool stage_body(const StageParams& p) {
             p.recv_rank_prefix[lane] = incl;
             ctrl[L.ctrl_recv_prefix() + lane] = incl - n;
             ctrl[L.ctrl_src_tokens() + lane] = ld_relaxed_sys(in + lane * msg + 1);
-            ctrl[L.ctrl_row_cursor() + lane] = 0;
         }
         if (lane == R - 1) {
             ctrl[L.ctrl_recv_prefix() + R] = incl;

@@ -66,7 +66,7 @@ struct WindowLayout {
     // words 4..6: status
     static constexpr int kTicketStage = 0, kTicketCombine = 1, kGoWord = 2, kTicketCopy = 3, kTicketPlan = 7, kGoWordPlan = 8, kCtrlHeaderInts = 16;
     NEP_HD int64_t ctrl_count_acc() const { return kCtrlHeaderInts; }                         // i32[R + E]
-    NEP_HD int64_t ctrl_row_cursor() const { return ctrl_count_acc() + ranks + num_experts; }  // i32[R]
+    NEP_HD int64_t ctrl_row_cursor() const { return ctrl_count_acc() + ranks + num_experts; }  // i32[R] (reserved; rows are placed by chunk prefixes)
     NEP_HD int64_t ctrl_expert_cursor() const { return ctrl_row_cursor() + ranks; }            // i32[L]
     NEP_HD int64_t ctrl_recv_prefix() const { return ctrl_expert_cursor() + local_experts; }   // i32[R+1] exclusive
     NEP_HD int64_t ctrl_expert_offsets() const { return ctrl_recv_prefix() + ranks + 1; }      // i32[L+1]

@@ -174,12 +174,12 @@ struct Streams {
 // behind `previous_event`).  Synchronous operations run directly on the caller's stream - no stream
 // hop on either side, which is what small (decode-size) calls are made of - after whatever earlier
 // asynchronous operation is still on the communication stream, so operations of one rank never overlap.
-// Two reusable events per thread for the stream hand-overs below (creating and destroying an event
-// per call costs microseconds, which small calls notice).
-cudaEvent_t handover_event(int slot) {
-    static thread_local cudaEvent_t events[2] = {nullptr, nullptr};
-    if (events[slot] == nullptr) cuda_check(cudaEventCreateWithFlags(&events[slot], cudaEventDisableTiming), "cudaEventCreate");
-    return events[slot];
+// A reusable event per thread for the stream hand-over below (creating and destroying an event per call
+// costs microseconds, which small calls notice).
+cudaEvent_t handover_event() {
+    static thread_local cudaEvent_t event = nullptr;
+    if (event == nullptr) cuda_check(cudaEventCreateWithFlags(&event, cudaEventDisableTiming), "cudaEventCreate");
+    return event;
 }
 
 Streams order_inputs(const std::vector<PeerWindow*>& wins, int64_t comm_handle, int64_t previous_event, int device, bool async_op) {
@@ -190,7 +190,7 @@ Streams order_inputs(const std::vector<PeerWindow*>& wins, int64_t comm_handle, 
         if (previous_event != -1) {
             cuda_check(cudaStreamWaitEvent(comm.stream(), reinterpret_cast<cudaEvent_t>(previous_event), 0), "wait previous_event");
         } else {
-            cudaEvent_t ready = handover_event(0);
+            cudaEvent_t ready = handover_event();
             cuda_check(cudaEventRecord(ready, compute.stream()), "record caller stream");
             cuda_check(cudaStreamWaitEvent(comm.stream(), ready, 0), "wait caller stream");
         }
