@@ -240,15 +240,18 @@ def verify_round_trip(args, buf, rank, world, device, control_group, x, idx, w, 
     lo = rank * L
     got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=expand, alignment=args.alignment, zero_padding=expand, num_sms=args.num_sms)
     back = buf.combine(got.x, got.handle, num_sms=args.num_sms)
-    torch.cuda.synchronize()
-    buf.check_status()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    if hasattr(buf, "check_status"):
+        buf.check_status()
     problems = []
-    # every rank's tokens and routing (over NCCL: device tensors)
+    # every rank's tokens and routing (device tensors over NCCL on GPUs; the control group on a CPU backend)
     all_x = torch.empty((world, T, H), dtype=x.dtype, device=device)
     all_idx = torch.empty((world, T, K), dtype=idx.dtype, device=device)
     if world > 1:
-        dist.all_gather_into_tensor(all_x, x)
-        dist.all_gather_into_tensor(all_idx, idx)
+        data_group = None if device.type == "cuda" else control_group
+        dist.all_gather(list(all_x.unbind(0)), x, group=data_group)
+        dist.all_gather(list(all_idx.unbind(0)), idx, group=data_group)
     else:
         all_x[0], all_idx[0] = x, idx
     mine = (all_idx >= lo) & (all_idx < lo + L)
