@@ -237,3 +237,20 @@ def test_barrier_timeout_is_reported_not_fatal():
     finally:
         torch.cuda.synchronize()
         group.close()
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 70), (4, 200), (8, 33)])
+def test_receive_rows_follow_source_and_token_order(world, tokens):
+    """A fresh dispatch places its receive rows by (source rank, source token): chunk prefixes, no atomics.  The combine
+    relies on it (rows of one source token then arrive from all expert ranks at about the same time)."""
+    case = make_case(world, kind="random", seed=21, hidden=256, tokens=tokens)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+    with EmulatedGroup(world, cfg) as group:
+        for expand in (False, True):
+            got = group.dispatch(_to_cuda(case.xs), topk_idx=_to_cuda(case.indices), do_expand=expand, alignment=4 if expand else 1)
+            torch.cuda.synchronize()
+            group.check_status()
+            for r in range(world):
+                meta = got[r].handle.layout.recv_metadata.cpu().long()
+                key = meta[:, 0] * (tokens + 1) + meta[:, 1]
+                assert (key[1:] > key[:-1]).all(), f"rank {r}: receive rows are not in (source, token) order"
