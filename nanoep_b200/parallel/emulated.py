@@ -33,6 +33,8 @@ class EmulatedGroup:
             raise ValueError("world size must be a power of two in [1, 32]")
         if config.num_experts % world_size:
             raise ValueError("num_experts must be divisible by world_size")
+        if config.hidden % 256:
+            raise ValueError("hidden must be a multiple of 256 (the kernels move rows in whole 32-lane passes of 16-byte chunks)")
         self.config = config
         self.world_size = world_size
         self.allow_multiple_reduction = allow_multiple_reduction
