@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import importlib
 import importlib.util
+import os
 import shutil
 import sys
 from pathlib import Path
@@ -52,10 +53,15 @@ def drop_peer_device_checks() -> None:
     (REF_OUT / "PEER_CHECKS_REMOVED").write_text("peer.cu:114-125 removed from the staged copy\n")
 
 
-def build(checkout: Path = Path("/root/reference"), verbose: bool = False, skip_peer_device_checks: bool = False):
+def build(checkout: Path | None = None, verbose: bool = False, skip_peer_device_checks: bool = False):
     import torch  # noqa: F401
     from torch.utils import cpp_extension
 
+    if checkout is None:
+        # where the reference checkout is mounted: NANOEP_REFERENCE_CHECKOUT, else a sibling "reference" of the repository
+        checkout = Path(os.environ.get("NANOEP_REFERENCE_CHECKOUT", HERE.parent.parent.parent / "reference"))
+    if not (checkout / "csrc" / "pipeline.cu").exists():
+        raise FileNotFoundError(f"no reference checkout at {checkout}; set NANOEP_REFERENCE_CHECKOUT")
     REF_OUT.mkdir(parents=True, exist_ok=True)
     marker = REF_OUT / "PEER_CHECKS_REMOVED"
     if marker.exists():

@@ -26,7 +26,7 @@ namespace nep {
 namespace {
 
 constexpr int kFusedDispatchDefaultTokens = 64;
-constexpr int kFusedFreshDefaultTokens = 0;  // single-launch fresh dispatch: off unless asked for (see DESIGN.md for the measurement)
+constexpr int kFusedFreshDefaultTokens = 0;  // single-launch fresh dispatch: off unless asked for (the host waits for N and C either way)
 constexpr int64_t kFusedFreshMaxOutputBytes = int64_t(256) << 20;  // single-launch fresh dispatch: largest bound-sized output
 constexpr int kFusedDefaultBlocks = 1024;  // i.e. bounded by the SM budget and co-residency only
 
