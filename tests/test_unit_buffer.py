@@ -314,3 +314,35 @@ def test_peer_access_rules():
     for can, supported in ((False, True), (True, False), (False, False)):
         unreachable = ext.peer_access_error(0, 1, 0, 4, can, supported)
         assert "no peer access" in unreachable and "device 4" in unreachable
+
+
+def test_single_launch_limits_round_trip():
+    """The run-time knobs of the single-launch dispatch paths: read, change one, keep the others, restore."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    before = ext.fused_limits()
+    assert len(before) == 3  # (cached dispatch tokens, grid bound, fresh dispatch tokens)
+    try:
+        ext.set_fused_limits(fresh_tokens=17)
+        assert ext.fused_limits() == (before[0], before[1], 17)
+        ext.set_fused_limits(dispatch_tokens=5, blocks=9)
+        assert ext.fused_limits() == (5, 9, 17)
+        ext.set_fused_limits()  # negative / omitted values keep what is there
+        assert ext.fused_limits() == (5, 9, 17)
+    finally:
+        ext.set_fused_limits(*before)
+    assert ext.fused_limits() == before
+
+
+def test_gate_hook_wants_pinned_host_memory():
+    import torch
+
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    import pytest
+
+    with pytest.raises(RuntimeError, match="pinned"):
+        ext.set_test_gate(torch.zeros(2, dtype=torch.int32), 1.0)  # pageable host memory: the kernel could not poll it
+    ext.set_test_gate(None)
