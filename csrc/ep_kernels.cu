@@ -173,9 +173,11 @@ __device__ bool stage_body(const StageParams& p) {
         // pull waits for these signals, nobody waits here.
         if (take_last_ticket(ctrl + WindowLayout::kTicketCopy)) {
             if (tid == 0) ctrl[WindowLayout::kTicketCopy] = 0;
-            __threadfence_system();
-            __syncthreads();
-            if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, R, L.data_signal_offset, p.epoch);
+            if (R > 1) {  // a single-rank group stages nothing and its pull waits for no signal
+                __threadfence_system();
+                __syncthreads();
+                if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, R, L.data_signal_offset, p.epoch);
+            }
         }
         stamp(2);
         if (!runs_tail) {
@@ -212,12 +214,18 @@ __device__ bool stage_body(const StageParams& p) {
         for (int i = tid; i < R + E; i += blockDim.x) count_acc[i] = 0;
     }
     if (tid == 0) ctrl[WindowLayout::kTicketStage] = 0;
-    __threadfence_system();
-    __syncthreads();
     __shared__ int s_ok;
-    if (warp == 0) {
-        const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagStage);
-        if (lane == 0) s_ok = ok;
+    if (R > 1) {
+        __threadfence_system();
+        __syncthreads();
+        if (warp == 0) {
+            const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagStage);
+            if (lane == 0) s_ok = ok;
+        }
+    } else {
+        // a single-rank group has nobody to wait for: its own messages are ordered by the block barrier below
+        __threadfence();
+        if (tid == 0) s_ok = 1;
     }
     __syncthreads();
     stamp(3);

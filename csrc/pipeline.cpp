@@ -432,7 +432,7 @@ DispatchOut dispatch(const std::vector<PeerWindow*>& wins, const std::vector<at:
             p.meta = fresh ? reinterpret_cast<const int*>(static_cast<char*>(wins[i]->base()) + L.meta_scratch_offset) : m[0].data_ptr<int>();
             p.rows = int(N);
             p.parity = parity[i];
-            p.data_epoch = fresh ? stage[i].epoch : 0;
+            p.data_epoch = (fresh && L.ranks > 1) ? stage[i].epoch : 0;  // a single-rank group pulls from the caller's tensor
             p.expand = expand;
             p.zero_padding = zero_padding;
             p.write_meta = fresh;
