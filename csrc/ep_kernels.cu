@@ -1226,6 +1226,11 @@ __device__ void local_combine_body(const LocalCombineParams& p) {
 }
 
 __device__ void barrier_body(const BarrierParams& p) {
+    if (p.signal_only) {
+        __threadfence_system();
+        peer_signal_warp(p.c.peers, p.c.rank, p.c.layout.ranks, p.c.layout.signal_offset, p.epoch);
+        return;
+    }
     peer_barrier_warp(p.c.peers, p.c.rank, p.c.layout.ranks, p.c.layout.signal_offset, p.epoch, p.c.timeout_ns, status_of(p.c),
                       kTagBarrier);
 }

@@ -157,6 +157,7 @@ struct LocalCombineParams {
 struct BarrierParams {
     CommonParams c;
     uint64_t epoch;
+    int signal_only;  // 1: publish the epoch to every peer and return (nobody waits here)
 };
 
 struct LaunchShape {

@@ -724,7 +724,7 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
         const int64_t T = meta[i][5].size(0);
         wins[i]->check_status();
         barrier[i].c = wins[i]->common();
-        barrier[i].epoch = wins[i]->begin_combine().epoch;  // a later combine waits for this barrier's epoch before it writes
+        barrier[i].epoch = wins[i]->reserve_epochs(1);
         TORCH_CHECK(L.ret_parts == L.topk, "this buffer's return area holds one partition per rank only");
         outs[i] = at::empty({T, L.hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device));
         ReduceParams& r = reduce[i];
@@ -747,6 +747,17 @@ std::vector<at::Tensor> combine_finish(const std::vector<PeerWindow*>& wins, con
     const ReduceParams* rdev = upload(reduce, keep, cs);
     PeerWindow::launches += 1;
     cuda_check(launch_reduce(rdev, LaunchShape{2 * lim.sms, n}, cs), "reduce launch");
+    // Tell every peer that this rank has finished reading its return area (nobody waits): the next combine kernel
+    // waits for this epoch before it overwrites the area, exactly as it does after a combine kernel.
+    std::vector<BarrierParams> done(n);
+    for (int i = 0; i < n; ++i) {
+        done[i].c = barrier[i].c;
+        done[i].epoch = wins[i]->begin_combine().epoch;
+        done[i].signal_only = 1;
+    }
+    const BarrierParams* ddev = upload(done, keep, cs);
+    PeerWindow::launches += 1;
+    cuda_check(launch_barrier(ddev, LaunchShape{1, n}, cs), "end-of-combine signal launch");
     return outs;
 }
 
