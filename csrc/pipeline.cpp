@@ -64,8 +64,14 @@ struct CombineTrace {
     bool enabled = false;
     at::Tensor words;  // uint64 x 4 as int64
     at::Tensor stage_words;  // uint64 x 5 as int64 (stage kernel of a fresh dispatch)
-    int depth = 0;     // 0 = kernel default
-    int group = 0;     // 0 = default reduce group size
+    // Tuning of the combine kernel: bulk stores pending per transfer warp and reduce warps per token (0 = default).
+    // NANOEP_COMBINE_STORE_DEPTH / NANOEP_COMBINE_REDUCE_GROUP set the process-wide start values.
+    int depth = 0;
+    int group = 0;
+    CombineTrace() {
+        if (const char* env = std::getenv("NANOEP_COMBINE_STORE_DEPTH")) depth = std::atoi(env);
+        if (const char* env = std::getenv("NANOEP_COMBINE_REDUCE_GROUP")) group = std::atoi(env);
+    }
 };
 CombineTrace g_trace;
 
