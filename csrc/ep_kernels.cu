@@ -143,32 +143,174 @@ __device__ bool stage_body(const StageParams& p) {
         stamp(1);
     }
 
-    // ---- rows: x and gate weights into this rank's staging area.  Work item = one quarter of a token row, so that
-    // even a few thousand tokens spread over the whole grid and every lane keeps up to eight 16-byte loads in flight.
-    if (!p.skip_copy) {
-        constexpr int kParts = 4;
-        const int per_part = (vecs + kParts - 1) / kParts;
-        for (int item = gw; item < p.tokens * kParts; item += GW) {
-            const int t = item / kParts, q = item % kParts;
-            const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
-            int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
-            const int end = min(vecs, (q + 1) * per_part);
-            for (int i = q * per_part + lane; i < end; i += 256) {
-                int4 v[8];
+    __shared__ int s_ok;
+    __shared__ int s_total[2];
+
+    auto copy_rows = [&]() {
+        // ---- rows: x and gate weights into this rank's staging area.  Work item = one quarter of a token row, so that
+        // even a few thousand tokens spread over the whole grid and every lane keeps up to eight 16-byte loads in flight.
+        if (!p.skip_copy) {
+            constexpr int kParts = 4;
+            const int per_part = (vecs + kParts - 1) / kParts;
+            for (int item = gw; item < p.tokens * kParts; item += GW) {
+                const int t = item / kParts, q = item % kParts;
+                const int4* src = reinterpret_cast<const int4*>(p.x + int64_t(t) * H);
+                int4* dst = reinterpret_cast<int4*>(rows + int64_t(t) * rb);
+                const int end = min(vecs, (q + 1) * per_part);
+                for (int i = q * per_part + lane; i < end; i += 256) {
+                    int4 v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (i + j * 32 < end) v[j] = ld_nc_v4(src + i + j * 32);
+                    for (int j = 0; j < 8; ++j)
+                        if (i + j * 32 < end) v[j] = ld_nc_v4(src + i + j * 32);
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (i + j * 32 < end) dst[i + j * 32] = v[j];
-            }
-            if (q == 0 && lane < K) {
-                const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
-                reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
+                    for (int j = 0; j < 8; ++j)
+                        if (i + j * 32 < end) dst[i + j * 32] = v[j];
+                }
+                if (q == 0 && lane < K) {
+                    const float w = p.weights != nullptr ? p.weights[int64_t(t) * K + lane] : 0.f;
+                    reinterpret_cast<float*>(rows + int64_t(t) * rb + wire_weights_offset(H))[lane] = w;
+                }
             }
         }
-    }
+    };
+
+    // The tail: run by ONE block per rank (the one that took the last ticket of the counting step, or of the copy in a
+    // cached dispatch).  Returns whether the peer barrier succeeded.
+    auto tail = [&]() -> bool {
+        // ---- tail: one block per rank
+        const int msg = int(L.msg_ints());
+        if (p.fresh) {
+            for (int i = tid; i < R * msg; i += blockDim.x) {
+                const int d = i / msg, j = i % msg;
+                const int v = j == 0 ? __ldcg(count_acc + d) : j == 1 ? p.tokens : __ldcg(count_acc + R + d * Le + (j - 2));
+                int* remote =
+                    reinterpret_cast<int*>(window(p.c, d) + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride) + p.c.rank * msg + j;
+                st_relaxed_sys(remote, v);
+            }
+            for (int d = tid; d < R; d += blockDim.x) p.send_counts[d] = __ldcg(count_acc + d);
+            // per-chunk row counts go to their destination (the accumulators are cleared for the next dispatch)
+            const int cps = int(L.chunks_per_rank()), my_chunks = (p.tokens + 31) / 32;
+            int* chunk_acc = ctrl + L.ctrl_chunk_acc();
+            for (int i = tid; i < R * my_chunks; i += blockDim.x) {
+                const int d = i / my_chunks, c = i % my_chunks;
+                int* remote = reinterpret_cast<int*>(window(p.c, d) + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride) + p.c.rank * cps + c;
+                st_relaxed_sys(remote, __ldcg(chunk_acc + d * cps + c));
+                chunk_acc[d * cps + c] = 0;
+            }
+            __syncthreads();
+            for (int i = tid; i < R + E; i += blockDim.x) count_acc[i] = 0;
+        }
+        if (tid == 0) ctrl[WindowLayout::kTicketStage] = 0;
+        if (R > 1) {
+            __threadfence_system();
+            __syncthreads();
+            if (warp == 0) {
+                const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagStage);
+                if (lane == 0) s_ok = ok;
+            }
+        } else {
+            // a single-rank group has nobody to wait for: its own messages are ordered by the block barrier below
+            __threadfence();
+            if (tid == 0) s_ok = 1;
+        }
+        __syncthreads();
+        stamp(3);
+        if (p.fused && !p.fresh) {
+            if (tid == 0) publish_go(ctrl, p.epoch, s_ok != 0);
+            return s_ok != 0;
+        }
+        if (!p.fresh) return s_ok != 0;
+        if (!s_ok) {
+            if (tid == 0) {
+                p.mailbox[1] = -2;
+                p.mailbox[0] = -2;
+                __threadfence_system();
+                if (p.fused) publish_go(ctrl, p.epoch, false);
+            }
+            return false;
+        }
+        const int* in = reinterpret_cast<const int*>(win + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride);
+        // Phase 1 (all threads): per local expert, sum the sources' counts and round up to the alignment.
+        // The padded sizes reuse the dynamic shared array (R + E ints >= L ints).
+        int* s_padded = s_counts;
+        for (int l = tid; l < Le; l += blockDim.x) {
+            int cnt = 0;
+            for (int src = 0; src < R; ++src) cnt += ld_relaxed_sys(in + src * msg + 2 + l);
+            p.expert_counts[l] = cnt;
+            ctrl[L.ctrl_expert_counts() + l] = cnt;
+            ctrl[L.ctrl_expert_cursor() + l] = 0;
+            s_padded[l] = (cnt + p.alignment - 1) / p.alignment * p.alignment;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // receive rows by source: inclusive prefix (R <= 32)
+            const int n = lane < R ? ld_relaxed_sys(in + lane * msg) : 0;
+            const int incl = warp_inclusive_sum(n);
+            if (lane < R) {
+                p.recv_rank_prefix[lane] = incl;
+                ctrl[L.ctrl_recv_prefix() + lane] = incl - n;
+                ctrl[L.ctrl_src_tokens() + lane] = ld_relaxed_sys(in + lane * msg + 1);
+            }
+            if (lane == R - 1) {
+                ctrl[L.ctrl_recv_prefix() + R] = incl;
+                s_total[0] = incl;
+            }
+        } else if (warp == 1) {
+            // Phase 2: exclusive scan of the padded sizes in waves of 32 (shared memory only)
+            int carry = 0;
+            for (int base = 0; base < Le; base += 32) {
+                const int l = base + lane;
+                const int padded = l < Le ? s_padded[l] : 0;
+                const int incl = warp_inclusive_sum(padded);
+                if (l < Le) {
+                    const int off = carry + incl - padded;
+                    p.expert_offsets[l] = off;
+                    ctrl[L.ctrl_expert_offsets() + l] = off;
+                }
+                carry += __shfl_sync(kFull, incl, 31);
+            }
+            if (lane == 0) {
+                p.expert_offsets[Le] = carry;
+                ctrl[L.ctrl_expert_offsets() + Le] = carry;
+                s_total[1] = carry;
+            }
+        }
+        // Every source's per-chunk row counts become exclusive prefixes: chunk c of source s starts at receive row
+        // recv_prefix[s] + chunk_prefix[s][c].  The total must equal the source's announced row count.
+        {
+            const int cps = int(L.chunks_per_rank());
+            int* chunks = reinterpret_cast<int*>(win + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride);
+            for (int s = warp; s < R; s += wpb) {
+                const int n_chunks = (ld_relaxed_sys(in + s * msg + 1) + 31) / 32;
+                int carry = 0;
+                for (int base = 0; base < n_chunks; base += 32) {
+                    const int c = base + lane;
+                    const int v = c < n_chunks ? ld_relaxed_sys(chunks + s * cps + c) : 0;
+                    const int incl = warp_inclusive_sum(v);
+                    if (c < n_chunks) chunks[s * cps + c] = carry + incl - v;
+                    carry += __shfl_sync(kFull, incl, 31);
+                }
+                if (lane == 0 && carry != ld_relaxed_sys(in + s * msg)) report(status, kSlotOverflow, uint32_t(s), kTagStage);
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            p.mailbox[1] = s_total[1];
+            p.mailbox[0] = s_total[0];
+            __threadfence_system();
+            if (p.fused) publish_go(ctrl, p.epoch, true);  // the other blocks of a single-launch dispatch go on to plan
+        }
+        stamp(4);
+        return true;
+    };
+
     if (p.fresh) {
+        // The count exchange comes first: every rank and the host wait for it.  The rows are staged underneath it by all
+        // the other blocks; the tail block copies its own small share afterwards.
+        bool ok = true;
+        if (runs_tail) ok = tail();
+        copy_rows();
         // The block that finishes its rows last tells every peer that this rank's rows are staged; the receivers'
         // pull waits for these signals, nobody waits here.
         if (take_last_ticket(ctrl + WindowLayout::kTicketCopy)) {
@@ -180,144 +322,17 @@ __device__ bool stage_body(const StageParams& p) {
             }
         }
         stamp(2);
-        if (!runs_tail) {
-            // single-launch fresh dispatch: wait for the tail block's prefixes before planning
-            if (!p.fused) return false;
-            return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
-        }
-    } else if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
+        if (runs_tail) return ok;
+        // single-launch fresh dispatch: wait for the tail block's prefixes before planning
         if (!p.fused) return false;
         return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
     }
-
-    // ---- tail: one block per rank
-    const int msg = int(L.msg_ints());
-    if (p.fresh) {
-        for (int i = tid; i < R * msg; i += blockDim.x) {
-            const int d = i / msg, j = i % msg;
-            const int v = j == 0 ? __ldcg(count_acc + d) : j == 1 ? p.tokens : __ldcg(count_acc + R + d * Le + (j - 2));
-            int* remote =
-                reinterpret_cast<int*>(window(p.c, d) + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride) + p.c.rank * msg + j;
-            st_relaxed_sys(remote, v);
-        }
-        for (int d = tid; d < R; d += blockDim.x) p.send_counts[d] = __ldcg(count_acc + d);
-        // per-chunk row counts go to their destination (the accumulators are cleared for the next dispatch)
-        const int cps = int(L.chunks_per_rank()), my_chunks = (p.tokens + 31) / 32;
-        int* chunk_acc = ctrl + L.ctrl_chunk_acc();
-        for (int i = tid; i < R * my_chunks; i += blockDim.x) {
-            const int d = i / my_chunks, c = i % my_chunks;
-            int* remote = reinterpret_cast<int*>(window(p.c, d) + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride) + p.c.rank * cps + c;
-            st_relaxed_sys(remote, __ldcg(chunk_acc + d * cps + c));
-            chunk_acc[d * cps + c] = 0;
-        }
-        __syncthreads();
-        for (int i = tid; i < R + E; i += blockDim.x) count_acc[i] = 0;
+    copy_rows();
+    if (!take_last_ticket(ctrl + WindowLayout::kTicketStage)) {
+        if (!p.fused) return false;
+        return wait_go(ctrl, p.epoch, p.c.timeout_ns, status, kTagStage);
     }
-    if (tid == 0) ctrl[WindowLayout::kTicketStage] = 0;
-    __shared__ int s_ok;
-    if (R > 1) {
-        __threadfence_system();
-        __syncthreads();
-        if (warp == 0) {
-            const bool ok = peer_barrier_warp(p.c.peers, p.c.rank, R, L.signal_offset, p.epoch, p.c.timeout_ns, status, kTagStage);
-            if (lane == 0) s_ok = ok;
-        }
-    } else {
-        // a single-rank group has nobody to wait for: its own messages are ordered by the block barrier below
-        __threadfence();
-        if (tid == 0) s_ok = 1;
-    }
-    __syncthreads();
-    stamp(3);
-    if (p.fused && !p.fresh) {
-        if (tid == 0) publish_go(ctrl, p.epoch, s_ok != 0);
-        return s_ok != 0;
-    }
-    if (!p.fresh) return s_ok != 0;
-    if (!s_ok) {
-        if (tid == 0) {
-            p.mailbox[1] = -2;
-            p.mailbox[0] = -2;
-            __threadfence_system();
-            if (p.fused) publish_go(ctrl, p.epoch, false);
-        }
-        return false;
-    }
-    const int* in = reinterpret_cast<const int*>(win + L.counts_in_offset + int64_t(p.parity) * L.counts_in_stride);
-    __shared__ int s_total[2];
-    // Phase 1 (all threads): per local expert, sum the sources' counts and round up to the alignment.
-    // The padded sizes reuse the dynamic shared array (R + E ints >= L ints).
-    int* s_padded = s_counts;
-    for (int l = tid; l < Le; l += blockDim.x) {
-        int cnt = 0;
-        for (int src = 0; src < R; ++src) cnt += ld_relaxed_sys(in + src * msg + 2 + l);
-        p.expert_counts[l] = cnt;
-        ctrl[L.ctrl_expert_counts() + l] = cnt;
-        ctrl[L.ctrl_expert_cursor() + l] = 0;
-        s_padded[l] = (cnt + p.alignment - 1) / p.alignment * p.alignment;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // receive rows by source: inclusive prefix (R <= 32)
-        const int n = lane < R ? ld_relaxed_sys(in + lane * msg) : 0;
-        const int incl = warp_inclusive_sum(n);
-        if (lane < R) {
-            p.recv_rank_prefix[lane] = incl;
-            ctrl[L.ctrl_recv_prefix() + lane] = incl - n;
-            ctrl[L.ctrl_src_tokens() + lane] = ld_relaxed_sys(in + lane * msg + 1);
-        }
-        if (lane == R - 1) {
-            ctrl[L.ctrl_recv_prefix() + R] = incl;
-            s_total[0] = incl;
-        }
-    } else if (warp == 1) {
-        // Phase 2: exclusive scan of the padded sizes in waves of 32 (shared memory only)
-        int carry = 0;
-        for (int base = 0; base < Le; base += 32) {
-            const int l = base + lane;
-            const int padded = l < Le ? s_padded[l] : 0;
-            const int incl = warp_inclusive_sum(padded);
-            if (l < Le) {
-                const int off = carry + incl - padded;
-                p.expert_offsets[l] = off;
-                ctrl[L.ctrl_expert_offsets() + l] = off;
-            }
-            carry += __shfl_sync(kFull, incl, 31);
-        }
-        if (lane == 0) {
-            p.expert_offsets[Le] = carry;
-            ctrl[L.ctrl_expert_offsets() + Le] = carry;
-            s_total[1] = carry;
-        }
-    }
-    // Every source's per-chunk row counts become exclusive prefixes: chunk c of source s starts at receive row
-    // recv_prefix[s] + chunk_prefix[s][c].  The total must equal the source's announced row count.
-    {
-        const int cps = int(L.chunks_per_rank());
-        int* chunks = reinterpret_cast<int*>(win + L.chunks_in_offset + int64_t(p.parity) * L.chunks_in_stride);
-        for (int s = warp; s < R; s += wpb) {
-            const int n_chunks = (ld_relaxed_sys(in + s * msg + 1) + 31) / 32;
-            int carry = 0;
-            for (int base = 0; base < n_chunks; base += 32) {
-                const int c = base + lane;
-                const int v = c < n_chunks ? ld_relaxed_sys(chunks + s * cps + c) : 0;
-                const int incl = warp_inclusive_sum(v);
-                if (c < n_chunks) chunks[s * cps + c] = carry + incl - v;
-                carry += __shfl_sync(kFull, incl, 31);
-            }
-            if (lane == 0 && carry != ld_relaxed_sys(in + s * msg)) report(status, kSlotOverflow, uint32_t(s), kTagStage);
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence_system();
-        p.mailbox[1] = s_total[1];
-        p.mailbox[0] = s_total[0];
-        __threadfence_system();
-        if (p.fused) publish_go(ctrl, p.epoch, true);  // the other blocks of a single-launch dispatch go on to plan
-    }
-    stamp(4);
-    return true;
+    return tail();
 }
 
 // ------------------------------------------------------------------------------------------
