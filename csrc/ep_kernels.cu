@@ -928,11 +928,12 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
         c.left &= c.left - 1;
         return true;
     };
+    const uint64_t once = l2_evict_first_policy();  // expert rows are read exactly once: keep L2 for the return rows
     auto issue = [&](const Cursor& c, int q) {
         const int y_row = by_slot ? __shfl_sync(kFull, c.v, c.k) : c.r;
         if (lane == 0) {
             mbar_expect_tx(ring.bar(q), xb);
-            bulk_load(ring.slot(q), p.y + int64_t(y_row) * H, xb, ring.bar(q));
+            bulk_load_hint(ring.slot(q), p.y + int64_t(y_row) * H, xb, ring.bar(q), once);
         }
     };
     Cursor ahead{-1, 0u, 0u, 0, -1, 0, 0, 0}, now{-1, 0u, 0u, 0, -1, 0, 0, 0};
@@ -983,7 +984,7 @@ __device__ __forceinline__ unsigned expected_parts(const int64_t* topk, int t, i
 // FP32 sum of the partitions in `parts` for the 16-byte column chunks `first`, `first + step`, ... of token t.
 // All partitions of a chunk are loaded before any is added, two chunks at a time.
 __device__ __forceinline__ void reduce_columns(const CommonParams& c, int t, unsigned parts, int my_part, const __nv_bfloat16* bias,
-                                               __nv_bfloat16* out, int first_base, int step) {
+                                               __nv_bfloat16* out, int first_base, int step, uint64_t once) {
     const WindowLayout& L = c.layout;
     const int H = L.hidden, lane = threadIdx.x & 31;
     const int vecs = H / 8;
@@ -1010,8 +1011,8 @@ __device__ __forceinline__ void reduce_columns(const CommonParams& c, int t, uns
             for (int j = 0; j < 8; ++j) {
                 if (part[j] >= 0) {
                     const int4* src = reinterpret_cast<const int4*>(row0 + part[j] * part_stride);
-                    if (one) d0[j] = ld_cg_v4(src + col);
-                    if (two) d1[j] = ld_cg_v4(src + col + step);
+                    if (one) d0[j] = ld_cg_v4_hint(src + col, once);
+                    if (two) d1[j] = ld_cg_v4_hint(src + col + step, once);
                 }
             }
 #pragma unroll
@@ -1028,17 +1029,28 @@ __device__ __forceinline__ void reduce_columns(const CommonParams& c, int t, uns
             if (two) accumulate8(a1, ld_nc_v4(b + col + step));
         }
         int4* o = reinterpret_cast<int4*>(out + int64_t(t) * H);
-        if (one) o[col] = pack8(a0);
-        if (two) o[col + step] = pack8(a1);
+        if (one) st_v4_hint(o + col, pack8(a0), once);
+        if (two) st_v4_hint(o + col + step, pack8(a1), once);
     }
 }
 
+constexpr int kReduceFlowWords = 2 + 2 * (kCombineThreads / 32 + 1);
+
 // Reduce warps of the combine kernel.  They form groups of `reduce_group` warps; a group sums ONE source token at a
-// time, each lane its own column chunks, so that a token that has just become complete is finished in a few
-// microseconds (what is left of the kernel after the last row has landed is one such token per group).  The group's
-// first warp waits (bounded) until every partition the token expects carries this combine's tag and releases the
-// others through the group's named barrier.
-__device__ void combine_reduce_role(const CombineParams& p, int* abort_word) {
+// time, each lane its own column chunks.  The group's first warp waits (bounded) until every partition the token
+// expects carries this combine's tag and releases the others through the group's named barrier.
+//
+// How long one token takes decides how long the kernel runs after the last row has landed: under the load of the
+// transfers a group of two warps needs ~30 us per token (seven dependent batches of loads at ~4 us each), five warps
+// ~13 us, all ten ~9 us - but larger groups hold fewer tokens at a time and fall behind the arrivals, and handing only
+// the last tokens of a CTA to all of its warps measured slower as well (they are summed one after the other).
+//
+// `flow` is a small shared array: [0] the CTA's abort word (sticky), then two go/stop words per group.  The warp that waited writes "go" or "stop" into the word of the barrier's
+// parity BEFORE the barrier and everybody reads it AFTER the barrier, so all warps of a barrier take the same branch
+// (reading the sticky abort word instead would let two warps of one barrier see different values and strand one of
+// them at the next barrier, which has no time limit).
+__device__ void combine_reduce_role(const CombineParams& p, int* flow) {
+    int* abort_word = flow;
     const WindowLayout& L = p.c.layout;
     const int K = L.topk, Le = L.local_experts, E = int(L.num_experts);
     const int lane = threadIdx.x & 31;
@@ -1046,50 +1058,96 @@ __device__ void combine_reduce_role(const CombineParams& p, int* abort_word) {
     const int rwarp = (threadIdx.x >> 5) - p.push_warps - 1;
     const int G = p.reduce_group < 1 ? 1 : (p.reduce_group > RW ? RW : p.reduce_group);
     const int groups = RW / G, g = rwarp / G, wi = rwarp % G;
-    if (g >= groups) return;  // warps that do not fill a group idle
     const StatusRef status = status_of(p.c);
     const uint32_t tag = combine_tag(p.epoch);
     const uint32_t* flag_base = reinterpret_cast<const uint32_t*>(window(p.c, p.c.rank) + L.ret_flag_offset);
     const float* ret_w = reinterpret_cast<const float*>(window(p.c, p.c.rank) + L.ret_w_offset);
-    for (int t = blockIdx.x * groups + g; t < p.tokens; t += gridDim.x * groups) {
-        bool valid;
-        int dest;
-        const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
-        const int my_part = L.rank_indexed ? dest : lane;
-        if (parts != 0) {
-            if (wi == 0) {
-                const bool mine = (parts >> lane) & 1u;
-                const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
-                const uint64_t start = global_timer_ns();
-                uint32_t spins = 0;
-                bool arrived = false;
-                for (;;) {
-                    const bool here = !mine || ld_relaxed_sys_u32(flag) == tag;
-                    arrived = __all_sync(kFull, here);
-                    if (arrived) break;
-                    __nanosleep(200);
-                    if ((++spins & 15u) == 0u && __any_sync(kFull, global_timer_ns() - start > p.c.timeout_ns)) break;
-                }
-                // the polls were relaxed; one acquiring load of each flag orders the rows behind them
-                if (arrived && mine) (void)ld_acquire_sys_u32(flag);
-                __syncwarp();
-                if (!arrived && lane == 0) {
-                    report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
-                    *(volatile int*)abort_word = 1;  // a peer never delivered: stop reducing, the host reports the status
-                }
-            }
-            // named barrier 1 + g: this group's reduce warps only
-            if (G > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(G * 32) : "memory");
-            if (*(volatile int*)abort_word) return;
+    // returned rows are read once and the result is written once: both leave L2 first
+    const uint64_t once = l2_evict_first_policy();
+    unsigned waited = 0, worked = 0, longest = 0, summed = 0;  // nanoseconds (a kernel runs far below four seconds)
+    unsigned long long longest_at = 0, last_seen = 0;
+
+    // One warp waits for the token's rows (bounded); on a timeout it reports and raises the CTA's abort word.
+    auto await_rows = [&](int t, unsigned parts, int my_part) -> bool {
+        const bool mine = (parts >> lane) & 1u;
+        const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
+        const uint64_t start = global_timer_ns();
+        uint32_t spins = 0;
+        bool arrived = false;
+        for (;;) {
+            const bool here = !mine || ld_relaxed_sys_u32(flag) == tag;
+            arrived = __all_sync(kFull, here);
+            if (arrived) break;
+            __nanosleep(200);
+            if ((++spins & 15u) == 0u && __any_sync(kFull, global_timer_ns() - start > p.c.timeout_ns)) break;
         }
-        reduce_columns(p.c, t, parts, my_part, p.bias, p.out, wi * 32, G * 32);
-        if (wi == 0 && p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+        // the polls were relaxed; one acquiring load of each flag orders the rows behind them
+        if (arrived && mine) (void)ld_acquire_sys_u32(flag);
+        __syncwarp();
+        if (!arrived && lane == 0) {
+            report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
+            *(volatile int*)abort_word = 1;  // a peer never delivered: stop reducing, the host reports the status
+        }
+        return arrived;
+    };
+    auto sum_token = [&](int t, unsigned parts, int my_part, bool valid, bool first_warp, int first_base, int step, uint64_t t_wait) {
+        const uint64_t t_work = p.trace != nullptr ? global_timer_ns() : 0;
+        reduce_columns(p.c, t, parts, my_part, p.bias, p.out, first_base, step, once);
+        if (first_warp && p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+        if (p.trace != nullptr) {
+            const uint64_t t_done = global_timer_ns();
+            waited += unsigned(t_work - t_wait);
+            worked += unsigned(t_done - t_work);
+            if (unsigned(t_done - t_work) > longest) {
+                longest = unsigned(t_done - t_work);
+                longest_at = t_work;
+            }
+            last_seen = t_work;
+            ++summed;
+        }
+    };
+
+    // warps that do not fill a group sit out
+    if (g < groups) {
+        int* go = flow + 2 + 2 * g;
+        unsigned syncs = 0;
+        for (int t = blockIdx.x * groups + g; t < p.tokens; t += gridDim.x * groups) {
+            bool valid;
+            int dest;
+            const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
+            const int my_part = L.rank_indexed ? dest : lane;
+            const uint64_t t_wait = p.trace != nullptr ? global_timer_ns() : 0;
+            if (parts != 0) {
+                bool ok = true;
+                if (wi == 0) {
+                    ok = !*(volatile int*)abort_word && await_rows(t, parts, my_part);
+                    if (G > 1 && lane == 0) *(volatile int*)(go + (syncs & 1u)) = ok;
+                }
+                if (G > 1) {
+                    // named barrier 1 + g: this group's reduce warps only
+                    asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(G * 32) : "memory");
+                    ok = *(volatile int*)(go + (syncs & 1u)) != 0;
+                    ++syncs;
+                }
+                if (!ok) break;
+            }
+            sum_token(t, parts, my_part, valid, wi == 0, wi * 32, G * 32, t_wait);
+        }
+    }
+    if (p.trace != nullptr && (rwarp % G) == 0 && lane == 0) {
+        atomicAdd(p.trace + 4, (unsigned long long)waited);
+        atomicAdd(p.trace + 5, (unsigned long long)worked);
+        atomicAdd(p.trace + 6, (unsigned long long)summed);
+        const unsigned long long t0 = *(volatile unsigned long long*)p.trace;
+        atomicMax(p.trace + 7, ((unsigned long long)longest << 32) | (unsigned long long)unsigned(longest_at - t0));
+        atomicMax(p.trace + 8, last_seen);
     }
 }
 
 __device__ void combine_body(const CombineParams& p) {
     extern __shared__ __align__(128) char s_ring[];
-    __shared__ int s_enter, s_abort;
+    __shared__ int s_enter;
+    __shared__ int s_flow[kReduceFlowWords];  // see combine_reduce_role
     const WindowLayout& L = p.c.layout;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const StatusRef status = status_of(p.c);
@@ -1097,10 +1155,8 @@ __device__ void combine_body(const CombineParams& p) {
     // the flag board sits behind the transfer rings (plan_ring leaves room for it)
     FlagBoard* board = reinterpret_cast<FlagBoard*>(
         (reinterpret_cast<uintptr_t>(s_ring + (align_up(int64_t(L.hidden) * 2, 128) + 8) * int64_t(p.push_warps) * p.stages) + 15) & ~uintptr_t(15));
-    if (threadIdx.x == 0) {
-        s_enter = 1;
-        s_abort = 0;
-    }
+    if (threadIdx.x == 0) s_enter = 1;
+    if (threadIdx.x < kReduceFlowWords) s_flow[threadIdx.x] = 0;
     if (threadIdx.x < kMaxPushWarps) board->completed[threadIdx.x] = board->published[threadIdx.x] = board->finished[threadIdx.x] = 0;
     __syncthreads();
     if (p.wait_epoch != 0) {
@@ -1119,7 +1175,7 @@ __device__ void combine_body(const CombineParams& p) {
         else if (role == 2)
             combine_publish_role(p, board);
         else
-            combine_reduce_role(p, &s_abort);
+            combine_reduce_role(p, s_flow);
         if (p.trace != nullptr && lane == 0) atomicMax(p.trace + role, global_timer_ns());
     }
     // The last block out tells every peer that this rank is done with the combine (nobody waits here).  Rows and
@@ -1145,7 +1201,7 @@ __device__ void reduce_body(const ReduceParams& p) {
         bool valid;
         int dest;
         const unsigned parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
-        reduce_columns(p.c, t, parts, L.rank_indexed ? dest : lane, p.bias, p.out, 0, 32);
+        reduce_columns(p.c, t, parts, L.rank_indexed ? dest : lane, p.bias, p.out, 0, 32, l2_evict_first_policy());
         if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
     }
 }

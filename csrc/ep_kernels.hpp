@@ -121,8 +121,10 @@ struct CombineParams {
     int reduce_group;     // reduce warps that share one source token (1 .. reduce warps per CTA)
     int store_depth;      // bulk stores a transfer warp may have pending before it waits (2, 4, 6, 8 or 12; anything else means 2)
     // Optional diagnostics (null = off): [0] earliest start, [1] latest end of the transfer warps, [2] of the
-    // publisher warps, [3] of the reduce warps, as %globaltimer nanoseconds.  A kernel profiler cannot be
-    // attached to a multi-process run, and events cannot see inside one launch.
+    // publisher warps, [3] of the reduce warps, as %globaltimer nanoseconds; [4] nanoseconds the reduce groups spent
+    // waiting for arrivals, summed over groups, [5] nanoseconds they spent summing, [6] tokens summed, [7] the longest
+    // single token (nanoseconds in the upper half, its start after [0] in the lower), [8] when the last token's rows
+    // were seen.  A kernel profiler cannot be attached to a multi-process run, and events cannot see inside one launch.
     unsigned long long* trace;
 };
 

@@ -62,7 +62,7 @@ PhaseMarks g_marks;
 // every traced combine and read on request.
 struct CombineTrace {
     bool enabled = false;
-    at::Tensor words;  // uint64 x 4 as int64
+    at::Tensor words;  // uint64 x 9 as int64
     at::Tensor stage_words;  // uint64 x 5 as int64 (stage kernel of a fresh dispatch)
     // Tuning of the combine kernel: bulk stores pending per transfer warp and reduce warps per token (0 = default).
     // NANOEP_COMBINE_STORE_DEPTH / NANOEP_COMBINE_REDUCE_GROUP set the process-wide start values.
@@ -666,7 +666,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
                 p.reduce_group = g_trace.group > 0 ? g_trace.group : 2;
             }
             if (g_trace.enabled && n == 1) {
-                if (!g_trace.words.defined()) g_trace.words = at::empty({4}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
+                if (!g_trace.words.defined()) g_trace.words = at::empty({9}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
                 p.trace = reinterpret_cast<unsigned long long*>(g_trace.words.data_ptr<int64_t>());
             }
             TORCH_CHECK(p.sum_all_choices == 0 || L.ret_parts == L.topk, "this buffer's return area holds one partition per rank only");
@@ -689,7 +689,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
         const int grid = int(std::max<int64_t>(1, std::min<int64_t>(cap, wanted)));
         const CombineParams* dev = upload(params, keep, cs);
         if (g_trace.enabled && n == 1) {
-            const int64_t init[4] = {INT64_MAX, 0, 0, 0};  // [0] takes the minimum, the others the maximum
+            const int64_t init[9] = {INT64_MAX, 0, 0, 0, 0, 0, 0, 0, 0};  // [0] takes the minimum, [1..3] and [7] the maximum, [4..6] are sums
             cuda_check(cudaMemcpyAsync(g_trace.words.data_ptr(), init, sizeof(init), cudaMemcpyHostToDevice, cs), "trace reset");
         }
         g_marks.mark("begin", cs);
@@ -811,6 +811,13 @@ std::vector<double> take_combine_trace() {
     const int64_t* w = host.data_ptr<int64_t>();
     if (w[0] == INT64_MAX) return out;
     for (int i = 1; i < 4; ++i) out.push_back(w[i] > w[0] ? double(w[i] - w[0]) * 1e-3 : 0.0);
+    // reduce groups: microseconds waited and summed (totals over all groups), tokens summed, longest token
+    out.push_back(double(w[4]) * 1e-3);
+    out.push_back(double(w[5]) * 1e-3);
+    out.push_back(double(w[6]));
+    out.push_back(double(uint64_t(w[7]) >> 32) * 1e-3);
+    out.push_back(double(uint64_t(w[7]) & 0xffffffffull) * 1e-3);  // when that token started
+    out.push_back(w[8] > w[0] ? double(w[8] - w[0]) * 1e-3 : 0.0);  // when the last token's rows were seen
     return out;
 }
 
