@@ -65,7 +65,8 @@ def parse_args():
     p.add_argument("--detail", action="store_true", help="record per-kernel device times (median, max over ranks) in phases_us")
     p.add_argument("--trace", action="store_true",
                    help="after the timed steps, run a few more with the kernels' own %%globaltimer stamps switched on and report them per rank "
-                        "in kernel_trace_us (combine: transfer warps done, flags published, reduce warps done; stage: routing counted, rows "
+                        "in kernel_trace_us (combine: transfer warps done, flags published, reduce warps done, then the reduce groups' totals: "
+                        "us waited, us summing, tokens, longest token, its start, last token's rows seen; stage: routing counted, rows "
                         "staged, peer barrier passed, tail done; microseconds from the kernel's first block)")
     return p.parse_args()
 
