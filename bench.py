@@ -424,7 +424,8 @@ def run_ours(args, rank, world, device, control_group):
 
         kernel_trace = None
         if args.trace:
-            ext.set_combine_trace(True, 0, 0)
+            knobs = (int(os.environ.get("NANOEP_COMBINE_STORE_DEPTH", 0)), int(os.environ.get("NANOEP_COMBINE_REDUCE_GROUP", 0)))
+            ext.set_combine_trace(True, *knobs)
             seen = {"combine": [], "stage": []}
             for i in range(12):
                 step(x_sets[i % len(x_sets)], idx, w)
@@ -434,7 +435,7 @@ def run_ours(args, rank, world, device, control_group):
                     seen["combine"].append(combine_stamps)
                     seen["stage"].append(stage_stamps)
                 dist.barrier(group=control_group)
-            ext.set_combine_trace(False, 0, 0)
+            ext.set_combine_trace(False, *knobs)
             mine = {k: [round(statistics.median(r[j] for r in rows), 1) for j in range(len(rows[0]))] if rows and rows[0] else []
                     for k, rows in seen.items()}
             gathered = [None] * world
