@@ -247,6 +247,37 @@ def back_to_back_combines(group, rank, world, multiple):
             assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16)), f"combine {it} of a back-to-back series is wrong"
 
 
+def traced_combine_reports_its_roles(group, rank, world):
+    """With the in-kernel time stamps switched on a combine still returns the exact sums, and the stamps are
+    consistent: transfers end before the last flag is out, every token is summed once, the roles end in order."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    case = make_case(world, kind="random", seed=61, hidden=512, tokens=57)
+    cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, 64)
+    with CudaBuffer(group, cfg, wait_timeout_s=30.0) as buf:
+        x, idx, w = case.xs[rank].cuda(), case.indices[rank].cuda(), case.weights[rank].cuda()
+        got = buf.dispatch(x, topk_idx=idx, weights=w, do_expand=True, alignment=8, zero_padding=True)
+        values = choice_values(case, seed=7)
+        y = expert_outputs(values, got, True)
+        ext.set_combine_trace(True, 0, 0)
+        try:
+            out = buf.combine(y, got.handle).x
+            torch.cuda.synchronize()
+            stamps = ext.take_combine_trace()
+        finally:
+            ext.set_combine_trace(False, 0, 0)
+        buf.check_status()
+        want = source_reference(values[rank], case.indices, rank, case.num_experts, world, expand=True, allow_multiple_reduction=False)
+        assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16)), "a traced combine returned different sums"
+        assert len(stamps) == 9, stamps
+        transfers, flags, reduced, waited, summing, tokens, longest, longest_at, last_seen = stamps
+        assert 0 < transfers <= flags + 1e-3 and 0 < reduced, stamps
+        assert tokens == case.xs[rank].shape[0], stamps
+        assert 0 < longest <= summing + 1e-3 and last_seen <= reduced + 1e-3 and longest_at <= reduced + 1e-3, stamps
+        assert waited >= 0, stamps
+
+
 def results_outlive_newer_operations(group, rank, world):
     """A slow consumer stream still reads a dispatch result after the caller dropped it and newer dispatches allocated
     tensors of the same sizes on the communication stream: the completion event registered the result with the
@@ -400,6 +431,7 @@ def main():
             slow_reader_keeps_its_rows(group, rank, world)
             results_outlive_newer_operations(group, rank, world)
             synchronous_operation_then_barrier(group, rank, world)
+            traced_combine_reports_its_roles(group, rank, world)
             for multiple in (False, True):
                 back_to_back_combines(group, rank, world, multiple)
             missing_peer_is_detected(group, rank, world)
