@@ -819,14 +819,29 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
     const WindowLayout& L = p.c.layout;
     const int R = L.ranks, K = L.topk, H = L.hidden;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, PW = p.push_warps;
-    const int gw = blockIdx.x * PW + warp, GW = gridDim.x * PW;
+    const int gw = blockIdx.x * PW + warp;
     const StatusRef status = status_of(p.c);
     const int MW = K + 2;
     const uint32_t xb = uint32_t(H) * 2u;
     Ring ring = make_ring(smem, PW, p.stages, xb);
     const int S = p.stages;
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
-    const int n_my = walk.items > gw ? (walk.items - gw + GW - 1) / GW : 0;
+    // The walk is shared by all transfer warps of the rank: a warp takes the next position from one counter when it
+    // needs work (the request for the position after that is already in flight).  Rows differ in how many transfers
+    // they need (0 to K local slots), so equal shares of rows would leave the warps with the most slots working
+    // alone at the end - with 44 transfers per warp on average the fullest of 740 warps has ~30 % more - while the
+    // links idle; with a shared position all warps end within one row of each other and rows leave in walk order.
+    int* work = ctrl_words(p.c) + WindowLayout::kWorkCursor;
+    int claimed = 0;  // lane 0: the position requested last
+    auto request = [&]() {
+        if (lane == 0) claimed = atomicAdd(work, 1);
+    };
+    auto take = [&]() {  // the requested position, on every lane; requests the one after it
+        const int v = __shfl_sync(kFull, claimed, 0);
+        if (v < walk.items) request();
+        return v;
+    };
+    request();
     const int depth = (p.store_depth == 4 || p.store_depth == 6 || p.store_depth == 8 || p.store_depth == 12) ? p.store_depth : 2;
     FlagWriter flags{board, warp, 0, depth, p.c.timeout_ns};
 
@@ -834,9 +849,11 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
         // FP32 sum of the row's local slots, one bf16 round, one store per (token, this rank).
         const int vecs = H / 8;
         int q = 0;  // rows sent so far: consecutive rows use consecutive ring stages
-        for (int i = 0; i < n_my; ++i) {
+        for (;;) {
+            const int item = take();
+            if (item >= walk.items) break;
             int r;
-            const bool live_row = walk.locate(gw + i * GW, r);
+            const bool live_row = walk.locate(item, r);
             const int* m = p.meta + int64_t(live_row ? r : 0) * MW;
             const int v = (live_row && lane < K) ? m[2 + lane] : -1;
             const unsigned vm = __ballot_sync(kFull, v >= 0 && v < p.capacity);
@@ -901,16 +918,27 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
     // compact layout = one per receive row; expert-major layout = one per local slot of the row.
     const bool by_slot = p.mode == kPushExpanded;
     struct Cursor {
-        int i;          // position in this warp's row sequence
         unsigned left;  // choices of the current row that still need a transfer
         unsigned vm;    // all valid choices of the current row
         int r, v, src, tok, k;
     };
-    auto next = [&](Cursor& c) {
+    // The loads run ahead of the stores over the same sequence of rows: the leading cursor takes positions from the
+    // shared counter and queues the live ones (lane n % 32 keeps the n-th), the trailing cursor reads them back.
+    int queued = 0, q_head = 0, q_tail = 0;
+    auto next = [&](Cursor& c, bool leading) {
         while (c.left == 0) {
-            if (++c.i >= n_my) return false;
             int r;
-            if (!walk.locate(gw + c.i * GW, r)) continue;
+            if (leading) {
+                const int item = take();
+                if (item >= walk.items) return false;
+                if (!walk.locate(item, r)) continue;
+                if (lane == (q_head & 31)) queued = r;
+                ++q_head;
+            } else {
+                if (q_tail == q_head) return false;
+                r = __shfl_sync(kFull, queued, q_tail & 31);
+                ++q_tail;
+            }
             const int* m = p.meta + int64_t(r) * MW;
             c.r = r;
             c.src = m[0];
@@ -936,11 +964,11 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
             bulk_load_hint(ring.slot(q), p.y + int64_t(y_row) * H, xb, ring.bar(q), once);
         }
     };
-    Cursor ahead{-1, 0u, 0u, 0, -1, 0, 0, 0}, now{-1, 0u, 0u, 0, -1, 0, 0, 0};
+    Cursor ahead{0u, 0u, 0, -1, 0, 0, 0}, now{0u, 0u, 0, -1, 0, 0, 0};
     int issued = 0;
     bool more = true;
-    while (issued < S - 1 && (more = next(ahead))) issue(ahead, issued++);
-    for (int q = 0; next(now); ++q) {
+    while (issued < S - 1 && (more = next(ahead, true))) issue(ahead, issued++);
+    for (int q = 0; next(now, false); ++q) {
         if (!ring.wait(q, p.c.timeout_ns)) {
             if (lane == 0) report(status, kCopyTimeout, uint32_t(gw), kTagPush);
             break;
@@ -957,7 +985,7 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
         }
         bulk_commit();
         flags.push(ret_flag(p.c, now.src, part, now.tok));
-        if (more && (more = next(ahead))) issue(ahead, issued++);
+        if (more && (more = next(ahead, true))) issue(ahead, issued++);
     }
     flags.finish();
 }
@@ -1182,7 +1210,10 @@ __device__ void combine_body(const CombineParams& p) {
     // flags are out already (completed bulk groups, the publishers' fences); the ticket orders this block's reads of
     // the return area before the signal that lets peers overwrite it.
     if (!take_last_ticket(ctrl + WindowLayout::kTicketCombine)) return;
-    if (threadIdx.x == 0) ctrl[WindowLayout::kTicketCombine] = 0;
+    if (threadIdx.x == 0) {
+        ctrl[WindowLayout::kTicketCombine] = 0;
+        ctrl[WindowLayout::kWorkCursor] = 0;  // every transfer warp of the rank is done: the next combine starts its walk at 0
+    }
     __threadfence_system();
     __syncthreads();
     if (warp == 0) peer_signal_warp(p.c.peers, p.c.rank, L.ranks, L.signal_offset, p.epoch);

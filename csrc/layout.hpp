@@ -63,8 +63,8 @@ struct WindowLayout {
     int64_t num_bytes;
 
     // ctrl sub-layout, in int32 units from ctrl_offset.
-    // words 4..6: status
-    static constexpr int kTicketStage = 0, kTicketCombine = 1, kGoWord = 2, kTicketCopy = 3, kTicketPlan = 7, kGoWordPlan = 8, kCtrlHeaderInts = 16;
+    // words 4..6: status; word 9: the combine's shared position in its row walk (reset by the combine's last block)
+    static constexpr int kTicketStage = 0, kTicketCombine = 1, kGoWord = 2, kTicketCopy = 3, kTicketPlan = 7, kGoWordPlan = 8, kWorkCursor = 9, kCtrlHeaderInts = 16;
     NEP_HD int64_t ctrl_count_acc() const { return kCtrlHeaderInts; }                         // i32[R + E]
     NEP_HD int64_t ctrl_row_cursor() const { return ctrl_count_acc() + ranks + num_experts; }  // i32[R] (reserved; rows are placed by chunk prefixes)
     NEP_HD int64_t ctrl_expert_cursor() const { return ctrl_row_cursor() + ranks; }            // i32[L]
