@@ -1172,6 +1172,178 @@ __device__ void combine_reduce_role(const CombineParams& p, int* flow) {
     }
 }
 
+// Bounded mbarrier wait of the reduce pipeline: also gives up as soon as the CTA's abort word is raised.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, uint64_t timeout_ns, const int* abort_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u && (*(volatile const int*)abort_word != 0 || global_timer_ns() - start > timeout_ns)) return false;
+    }
+    return true;
+}
+
+// Where the reduce pipeline's stages start in dynamic shared memory (behind the transfer rings and the flag board).
+__device__ __forceinline__ char* reduce_area(const CombineParams& p, char* smem) {
+    const int64_t ring_end = (align_up(int64_t(p.c.layout.hidden) * 2, 128) + 8) * int64_t(p.push_warps) * p.stages;
+    const uintptr_t board = (reinterpret_cast<uintptr_t>(smem + ring_end) + 15) & ~uintptr_t(15);
+    return reinterpret_cast<char*>((board + sizeof(FlagBoard) + 127) & ~uintptr_t(127));
+}
+
+// The source-side sum fed through shared memory.  The CTA sums ONE of its tokens at a time: the first reduce warp
+// (the loader) waits for the token's arrival flags and bulk-loads `reduce_chunk_bytes` of every expected partition
+// row into the next free stage of a small ring; the other reduce warps wait on the stage's mbarrier, add the rows
+// in FP32 in ascending partition order straight from shared memory, add the bias, round once and store.  A bulk load
+// keeps no registers busy, so all partitions of a chunk are in flight at once and several chunks ahead: what is left
+// of the kernel after the last row has landed is one load latency and a sum from shared memory, where the register
+// path needs seven dependent batches of loads per token.
+__device__ void combine_reduce_smem_role(const CombineParams& p, int* flow, char* area) {
+    int* abort_word = flow;
+    const WindowLayout& L = p.c.layout;
+    const int K = L.topk, Le = L.local_experts, E = int(L.num_experts), H = L.hidden, P = L.ret_parts;
+    const int lane = threadIdx.x & 31;
+    const int RW = (blockDim.x >> 5) - p.push_warps - 1;
+    const int rwarp = (threadIdx.x >> 5) - p.push_warps - 1;
+    const int CW = RW - 1;  // consumer warps
+    const int NS = p.reduce_stages, cw = p.reduce_chunk_bytes, xb = H * 2;
+    const int nc = (xb + cw - 1) / cw;
+    uint64_t* full = reinterpret_cast<uint64_t*>(area + int64_t(NS) * P * cw);
+    uint64_t* empty = full + NS;
+    const StatusRef status = status_of(p.c);
+    const uint32_t tag = combine_tag(p.epoch);
+    const int n_tok = p.tokens > int(blockIdx.x) ? (p.tokens - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const int units = n_tok * nc;
+    const uint64_t once = l2_evict_first_policy();
+
+    if (rwarp == 0) {
+        // ---- loader
+        const uint32_t* flag_base = reinterpret_cast<const uint32_t*>(window(p.c, p.c.rank) + L.ret_flag_offset);
+        const float* ret_w = reinterpret_cast<const float*>(window(p.c, p.c.rank) + L.ret_w_offset);
+        unsigned parts = 0;
+        int my_part = 0;
+        for (int u = 0; u < units; ++u) {
+            const int c = u % nc, t = int(blockIdx.x) + (u / nc) * int(gridDim.x);
+            const int s = u % NS, n = u / NS;
+            if (c == 0) {
+                bool valid;
+                int dest;
+                parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
+                my_part = L.rank_indexed ? dest : lane;
+                if (parts != 0) {
+                    const bool mine = (parts >> lane) & 1u;
+                    const uint32_t* flag = flag_base + int64_t(mine ? my_part : 0) * L.max_tokens + t;
+                    const uint64_t start = global_timer_ns();
+                    uint32_t spins = 0;
+                    bool arrived = false;
+                    for (;;) {
+                        const bool here = !mine || ld_relaxed_sys_u32(flag) == tag;
+                        arrived = __all_sync(kFull, here);
+                        if (arrived) break;
+                        __nanosleep(100);
+                        if ((++spins & 15u) == 0u &&
+                            __any_sync(kFull, *(volatile int*)abort_word != 0 || global_timer_ns() - start > p.c.timeout_ns))
+                            break;
+                    }
+                    // the polls were relaxed; one acquiring load of each flag orders the rows behind them, and the
+                    // proxy fence orders the bulk loads below behind that
+                    if (arrived && mine) (void)ld_acquire_sys_u32(flag);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (!arrived) {
+                        if (lane == 0) {
+                            report(status, kBarrierTimeout, uint32_t(t), kTagReduce);
+                            *(volatile int*)abort_word = 1;  // a peer never delivered: the consumers stop at their next wait
+                        }
+                        break;
+                    }
+                }
+                if (p.w_out != nullptr && lane < K) p.w_out[int64_t(t) * K + lane] = valid ? __ldcg(ret_w + int64_t(t) * K + lane) : 0.f;
+            }
+            if (n >= 1) {
+                // the stage is free once every consumer warp has read its previous contents
+                bool ok = mbar_wait_or_abort(empty + s, uint32_t(n - 1) & 1u, p.c.timeout_ns, abort_word);
+                ok = __all_sync(kFull, ok);
+                if (!ok) {
+                    if (lane == 0 && *(volatile int*)abort_word == 0) {
+                        report(status, kCopyTimeout, uint32_t(t), kTagReduce);
+                        *(volatile int*)abort_word = 1;
+                    }
+                    break;
+                }
+            }
+            const int bytes = min(cw, xb - c * cw);
+            if (lane == 0) mbar_expect_tx(full + s, uint32_t(__popc(parts) * bytes));
+            __syncwarp();
+            if ((parts >> lane) & 1u) {
+                const int j = __popc(parts & lanemask_lt());
+                bulk_load_hint(area + (int64_t(s) * P + j) * cw, ret_row(p.c, p.c.rank, my_part, t) + int64_t(c) * cw, uint32_t(bytes),
+                               full + s, once);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers
+    const int cwarp = rwarp - 1;
+    unsigned parts = 0;
+    unsigned waited = 0, worked = 0, longest = 0, summed = 0;  // nanoseconds
+    unsigned long long longest_at = 0, last_seen = 0;
+    for (int u = 0; u < units; ++u) {
+        const int c = u % nc, t = int(blockIdx.x) + (u / nc) * int(gridDim.x);
+        const int s = u % NS, n = u / NS;
+        if (c == 0) {
+            bool valid;
+            int dest;
+            parts = expected_parts(p.topk, t, K, E, Le, p.sum_all_choices != 0, valid, dest);
+        }
+        const uint64_t t_wait = p.trace != nullptr ? global_timer_ns() : 0;
+        {
+            bool ok = mbar_wait_or_abort(full + s, uint32_t(n) & 1u, p.c.timeout_ns, abort_word);
+            ok = __all_sync(kFull, ok);
+            if (!ok) {
+                if (lane == 0 && *(volatile int*)abort_word == 0) {
+                    report(status, kCopyTimeout, uint32_t(t), kTagReduce);
+                    *(volatile int*)abort_word = 1;
+                }
+                break;
+            }
+        }
+        const uint64_t t_work = p.trace != nullptr ? global_timer_ns() : 0;
+        const int np = __popc(parts);
+        const int bytes = min(cw, xb - c * cw);
+        const char* rows = area + int64_t(s) * P * cw;
+        for (int v = cwarp * 32 + lane; v * 16 < bytes; v += CW * 32) {
+            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int j = 0; j < np; ++j) accumulate8(a, *reinterpret_cast<const int4*>(rows + int64_t(j) * cw + v * 16));
+            const int64_t at = (int64_t(t) * xb + int64_t(c) * cw) / 16 + v;  // 16-byte units from the start of the output
+            if (p.bias != nullptr) accumulate8(a, ld_nc_v4(reinterpret_cast<const int4*>(p.bias) + at));
+            st_v4_hint(reinterpret_cast<int4*>(p.out) + at, pack8(a), once);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        if (p.trace != nullptr) {
+            const uint64_t t_done = global_timer_ns();
+            waited += unsigned(t_work - t_wait);
+            worked += unsigned(t_done - t_work);
+            if (unsigned(t_done - t_work) > longest) {
+                longest = unsigned(t_done - t_work);
+                longest_at = t_work;
+            }
+            last_seen = t_work;
+            summed += c == 0 ? 1u : 0u;
+        }
+    }
+    if (p.trace != nullptr && cwarp == 0 && lane == 0) {
+        atomicAdd(p.trace + 4, (unsigned long long)waited);
+        atomicAdd(p.trace + 5, (unsigned long long)worked);
+        atomicAdd(p.trace + 6, (unsigned long long)summed);
+        const unsigned long long t0 = *(volatile unsigned long long*)p.trace;
+        atomicMax(p.trace + 7, ((unsigned long long)longest << 32) | (unsigned long long)unsigned(longest_at - t0));
+        atomicMax(p.trace + 8, last_seen);
+    }
+}
+
 __device__ void combine_body(const CombineParams& p) {
     extern __shared__ __align__(128) char s_ring[];
     __shared__ int s_enter;
@@ -1183,7 +1355,21 @@ __device__ void combine_body(const CombineParams& p) {
     // the flag board sits behind the transfer rings (plan_ring leaves room for it)
     FlagBoard* board = reinterpret_cast<FlagBoard*>(
         (reinterpret_cast<uintptr_t>(s_ring + (align_up(int64_t(L.hidden) * 2, 128) + 8) * int64_t(p.push_warps) * p.stages) + 15) & ~uintptr_t(15));
-    if (threadIdx.x == 0) s_enter = 1;
+    if (threadIdx.x == 0) {
+        s_enter = 1;
+        if (p.reduce_stages >= 2) {
+            // full: the loader's arrival plus the bytes of its bulk loads; empty: one arrival per consumer warp
+            char* area = reduce_area(p, s_ring);
+            uint64_t* full = reinterpret_cast<uint64_t*>(area + int64_t(p.reduce_stages) * L.ret_parts * p.reduce_chunk_bytes);
+            const int consumers = int(blockDim.x >> 5) - p.push_warps - 2;
+            for (int s = 0; s < p.reduce_stages; ++s) {
+                mbar_init(full + s, 1);
+                mbar_init(full + p.reduce_stages + s, uint32_t(consumers));
+            }
+            mbar_init_fence();
+            fence_proxy_async_smem();
+        }
+    }
     if (threadIdx.x < kReduceFlowWords) s_flow[threadIdx.x] = 0;
     if (threadIdx.x < kMaxPushWarps) board->completed[threadIdx.x] = board->published[threadIdx.x] = board->finished[threadIdx.x] = 0;
     __syncthreads();
@@ -1202,6 +1388,8 @@ __device__ void combine_body(const CombineParams& p) {
             combine_push_role(p, s_ring, board);
         else if (role == 2)
             combine_publish_role(p, board);
+        else if (p.reduce_stages >= 2)
+            combine_reduce_smem_role(p, s_flow, reduce_area(p, s_ring));
         else
             combine_reduce_role(p, s_flow);
         if (p.trace != nullptr && lane == 0) atomicMax(p.trace + role, global_timer_ns());
@@ -1455,6 +1643,36 @@ RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes) {
     r.warps = warps > 8 ? 8 : warps;
     r.smem_bytes = size_t(r.warps) * r.stages * (pitch + 8) + kZeroBytes + 256;
     return r;
+}
+
+CombinePlan plan_combine(int64_t row_bytes, int parts, int max_smem_bytes, int reduce_stages, int reduce_chunk_bytes) {
+    // smem = transfer rings (warps x stages x (row pitch + mbarrier)) + flag board + reduce pipeline
+    // (stages x parts x chunk + two mbarriers per stage) + alignment slack + static smem.
+    CombinePlan c{};
+    const int64_t pitch = align_up(row_bytes, 128);
+    const int64_t fixed = int64_t(sizeof(FlagBoard)) + 16 + 128 + 512;
+    if (reduce_stages >= 2) {
+        int64_t chunk = reduce_chunk_bytes > 0 ? align_up(reduce_chunk_bytes, 128) : 0;
+        if (chunk == 0) {
+            // about half of shared memory for the pipeline, whole rows when they fit
+            chunk = (int64_t(max_smem_bytes) / 2 / reduce_stages / parts) / 128 * 128;
+        }
+        chunk = std::min<int64_t>(chunk, pitch);
+        if (chunk >= 128) {
+            c.reduce_stages = reduce_stages;
+            c.reduce_chunk_bytes = int(chunk);
+        }
+    }
+    const int64_t pipe = c.reduce_stages >= 2 ? int64_t(c.reduce_stages) * parts * c.reduce_chunk_bytes + 16 * c.reduce_stages : 0;
+    const int64_t slots = (int64_t(max_smem_bytes) - fixed - pipe) / (pitch + 8);
+    // three stages per transfer warp when there is room for at least four such warps, else two
+    c.ring.stages = slots >= 12 ? 3 : 2;
+    int64_t warps = slots / c.ring.stages;
+    // the register path needs reduce warps in whole groups; the pipeline a loader and at least one consumer warp
+    warps = std::min<int64_t>(warps, 8);
+    c.ring.warps = warps < 1 ? 0 : int(warps);
+    c.ring.smem_bytes = size_t(c.ring.warps) * c.ring.stages * (pitch + 8) + size_t(fixed - 256) + size_t(pipe);
+    return c;
 }
 
 cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream) {

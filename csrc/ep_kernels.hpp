@@ -118,7 +118,11 @@ struct CombineParams {
     int sum_all_choices;  // 1: one partition per valid k; 0: one per destination rank
     uint64_t epoch;       // signalled to every peer when this rank's pushes and reduction are done
     uint64_t wait_epoch;  // peers must have signalled this much before their return area is overwritten (0: nothing to wait for)
-    int reduce_group;     // reduce warps that share one source token (1 .. reduce warps per CTA)
+    int reduce_group;     // register path: reduce warps that share one source token (1 .. reduce warps per CTA)
+    // Shared-memory path of the source-side sum (reduce_stages >= 2; 0 selects the register path): the returned rows
+    // of a token are bulk-loaded into a ring of reduce_stages stages, reduce_chunk_bytes of every partition per stage.
+    int reduce_stages;
+    int reduce_chunk_bytes;
     int store_depth;      // bulk stores a transfer warp may have pending before it waits (2, 4, 6, 8 or 12; anything else means 2)
     // Optional diagnostics (null = off): [0] earliest start, [1] latest end of the transfer warps, [2] of the
     // publisher warps, [3] of the reduce warps, as %globaltimer nanoseconds; [4] nanoseconds the reduce groups spent
@@ -193,6 +197,13 @@ struct RingPlan {
     size_t smem_bytes;
 };
 RingPlan plan_ring(int64_t row_bytes, int max_smem_bytes);
+// Shared memory of a combine CTA: the transfer warps' rings, the flag board and (reduce_stages >= 2) the reduce
+// pipeline.  reduce_chunk_bytes == 0 lets the plan pick the chunk.
+struct CombinePlan {
+    RingPlan ring;
+    int reduce_stages, reduce_chunk_bytes;
+};
+CombinePlan plan_combine(int64_t row_bytes, int parts, int max_smem_bytes, int reduce_stages, int reduce_chunk_bytes);
 constexpr int kCombineThreads = 512;  // transfer warps + reduce warps of one combine CTA
 int stage_smem_bytes(const WindowLayout& l);
 int plan_smem_bytes(const WindowLayout& l);

@@ -74,6 +74,9 @@ struct CombineTrace {
     }
 };
 CombineTrace g_trace;
+// Shared-memory pipeline with two stages and a chunk of about half of shared memory / 2 / partitions (whole rows at
+// hidden 7168 x 8 partitions): same time as the register path at 4096 tokens per rank, 10-14 us less from 1 to 128.
+constexpr int kDefaultReduceSetting = -2000;
 
 // Test hook: while set, every dispatch of this process launches a gate kernel between its planning kernels and its
 // pull, so a test can keep one rank's pull pending (a "slow reader") while its peers run ahead.
@@ -575,7 +578,13 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
     }
     const DeviceLimits lim = device_limits();
     TORCH_CHECK(num_sms >= 1 && num_sms <= lim.sms, "num_sms out of range");
-    const RingPlan ring = plan_ring(int64_t(L.hidden) * 2, lim.smem_optin);
+    // How the source-side sum runs: a positive setting = register path with that many warps per token; a negative one
+    // = shared-memory pipeline, -(stages * 1000 + chunk bytes / 128) with chunk 0 = chosen by the plan; 0 = default.
+    const int reduce_setting = g_trace.group != 0 ? g_trace.group : kDefaultReduceSetting;
+    const int pipe_stages = reduce_setting < 0 ? (-reduce_setting) / 1000 : 0;
+    const int pipe_chunk = reduce_setting < 0 ? ((-reduce_setting) % 1000) * 128 : 0;
+    const CombinePlan plan = plan_combine(int64_t(L.hidden) * 2, L.ret_parts, lim.smem_optin, pipe_stages, pipe_chunk);
+    const RingPlan ring = plan.ring;
     TORCH_CHECK(ring.warps >= 1, "hidden size too large for the shared-memory row ring");
     reject_graph_capture(device, "barrier epochs and buffer parities are kernel arguments");
 
@@ -660,11 +669,11 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
             p.epoch = epochs.epoch;
             p.wait_epoch = epochs.wait_epoch;
             p.store_depth = g_trace.depth;
-            {
-                // Two reduce warps share a token by default (measured at 2 and 8 GPUs: one or two per token finish the
-                // kernel soonest; larger groups spend more on their barrier than they gain).
-                p.reduce_group = g_trace.group > 0 ? g_trace.group : 2;
-            }
+            // Register path: two reduce warps share a token (measured at 2 and 8 GPUs: one or two per token finish the
+            // kernel soonest; larger groups hold fewer tokens at a time).
+            p.reduce_group = reduce_setting > 0 ? reduce_setting : 2;
+            p.reduce_stages = plan.reduce_stages;
+            p.reduce_chunk_bytes = plan.reduce_chunk_bytes;
             if (g_trace.enabled && n == 1) {
                 if (!g_trace.words.defined()) g_trace.words = at::empty({9}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device));
                 p.trace = reinterpret_cast<unsigned long long*>(g_trace.words.data_ptr<int64_t>());
@@ -681,7 +690,7 @@ CombineOut combine(const std::vector<PeerWindow*>& wins, const std::vector<at::T
         }
         // Every block holds transfer warps and a group of reduce warps that sums one token at a time: enough blocks
         // for the larger of the two jobs.
-        const int groups = std::max(1, (kCombineThreads / 32 - ring.warps - 1) / params[0].reduce_group);
+        const int groups = plan.reduce_stages >= 2 ? 1 : std::max(1, (kCombineThreads / 32 - ring.warps - 1) / params[0].reduce_group);
         const int64_t wanted = std::max<int64_t>((max_transfers + ring.warps - 1) / ring.warps, (max_tokens_now + groups - 1) / groups);
         // A whole logical group in one launch waits on itself: all its blocks must be resident (cooperative launch).
         const bool group_launch = n > 1;
