@@ -64,7 +64,8 @@ struct CombineTrace {
     bool enabled = false;
     at::Tensor words;  // uint64 x 9 as int64
     at::Tensor stage_words;  // uint64 x 5 as int64 (stage kernel of a fresh dispatch)
-    // Tuning of the combine kernel: bulk stores pending per transfer warp and reduce warps per token (0 = default).
+    // Tuning of the combine kernel: bulk stores pending per transfer warp and the form of the source-side sum
+    // (see set_combine_trace); 0 = default.
     // NANOEP_COMBINE_STORE_DEPTH / NANOEP_COMBINE_REDUCE_GROUP set the process-wide start values.
     int depth = 0;
     int group = 0;

@@ -67,7 +67,9 @@ void set_fused_limits(int64_t dispatch_tokens, int64_t blocks, int64_t fresh_tok
 // In-kernel time stamps of the next combines of this process (single-rank calls): microseconds from the
 // kernel's first block to the end of its transfer warps, its flag publishers and its reduce warps.
 // `store_depth` (0 = default) sets how many bulk stores a transfer warp keeps pending, `reduce_group` (0 = default)
-// how many reduce warps share one source token.  take_combine_trace() returns those three stamps followed by the
+// how the source-side sum runs: N > 0 = in registers with N reduce warps per token, a negative value
+// -(stages * 1000 + chunk bytes / 128) = through a shared-memory ring of that many stages (chunk 0 = chosen by the
+// plan).  take_combine_trace() returns those three stamps followed by the
 // reduce groups' totals: microseconds waited, microseconds summing, tokens summed, the longest token, when it began
 // and when the last token's rows were seen.
 void set_combine_trace(bool enabled, int64_t store_depth, int64_t reduce_group);
