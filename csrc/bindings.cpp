@@ -175,6 +175,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_fused_limits", &nep::set_fused_limits, py::arg("dispatch_tokens") = -1, py::arg("blocks") = -1, py::arg("fresh_tokens") = -1);
     m.def("set_test_gate", &nep::set_test_gate, py::arg("word"), py::arg("timeout_s") = 10.0);
     m.def("set_phase_timing", &nep::set_phase_timing);
+    m.def(
+        "combine_plan",
+        [](int64_t hidden, int64_t parts, int64_t max_smem_bytes, int64_t reduce_stages, int64_t reduce_chunk_bytes) {
+            const nep::CombinePlan plan = nep::plan_combine(hidden * 2, int(parts), int(max_smem_bytes), int(reduce_stages), int(reduce_chunk_bytes));
+            return std::make_tuple(plan.ring.warps, plan.ring.stages, int64_t(plan.ring.smem_bytes), plan.reduce_stages, plan.reduce_chunk_bytes);
+        },
+        py::arg("hidden"), py::arg("parts"), py::arg("max_smem_bytes"), py::arg("reduce_stages") = 2, py::arg("reduce_chunk_bytes") = 0,
+        "Shared-memory plan of a combine CTA: (transfer warps, ring stages, dynamic bytes, reduce stages, reduce chunk bytes)");
     m.def("set_combine_trace", &nep::set_combine_trace, py::arg("enabled"), py::arg("store_depth") = 0, py::arg("reduce_group") = 0);
     m.def("take_combine_trace", &nep::take_combine_trace);
     m.def("take_stage_trace", &nep::take_stage_trace);

@@ -1651,28 +1651,38 @@ CombinePlan plan_combine(int64_t row_bytes, int parts, int max_smem_bytes, int r
     CombinePlan c{};
     const int64_t pitch = align_up(row_bytes, 128);
     const int64_t fixed = int64_t(sizeof(FlagBoard)) + 16 + 128 + 512;
+    int64_t chunk = 0;
     if (reduce_stages >= 2) {
-        int64_t chunk = reduce_chunk_bytes > 0 ? align_up(reduce_chunk_bytes, 128) : 0;
-        if (chunk == 0) {
-            // about half of shared memory for the pipeline, whole rows when they fit
-            chunk = (int64_t(max_smem_bytes) / 2 / reduce_stages / parts) / 128 * 128;
-        }
+        // about half of shared memory for the pipeline unless the caller names a chunk; whole rows when they fit
+        chunk = reduce_chunk_bytes > 0 ? align_up(reduce_chunk_bytes, 128) : (int64_t(max_smem_bytes) / 2 / reduce_stages / parts) / 128 * 128;
         chunk = std::min<int64_t>(chunk, pitch);
-        if (chunk >= 128) {
-            c.reduce_stages = reduce_stages;
-            c.reduce_chunk_bytes = int(chunk);
-        }
     }
-    const int64_t pipe = c.reduce_stages >= 2 ? int64_t(c.reduce_stages) * parts * c.reduce_chunk_bytes + 16 * c.reduce_stages : 0;
-    const int64_t slots = (int64_t(max_smem_bytes) - fixed - pipe) / (pitch + 8);
-    // three stages per transfer warp when there is room for at least four such warps, else two
-    c.ring.stages = slots >= 12 ? 3 : 2;
-    int64_t warps = slots / c.ring.stages;
-    // the register path needs reduce warps in whole groups; the pipeline a loader and at least one consumer warp
-    warps = std::min<int64_t>(warps, 8);
-    c.ring.warps = warps < 1 ? 0 : int(warps);
-    c.ring.smem_bytes = size_t(c.ring.warps) * c.ring.stages * (pitch + 8) + size_t(fixed - 256) + size_t(pipe);
-    return c;
+    // transfer warps the rings would get without a pipeline: an automatic chunk shrinks rather than take the second one
+    const int64_t alone = std::min<int64_t>((int64_t(max_smem_bytes) - fixed) / (pitch + 8) / 2, 8);
+    for (;;) {
+        const bool piped = reduce_stages >= 2 && chunk >= 128;
+        const int64_t pipe = piped ? int64_t(reduce_stages) * parts * chunk + 16 * reduce_stages : 0;
+        const int64_t slots = (int64_t(max_smem_bytes) - fixed - pipe) / (pitch + 8);
+        // three stages per transfer warp when there is room for at least four such warps, else two
+        const int stages = slots >= 12 ? 3 : 2;
+        const int64_t warps = std::min<int64_t>(slots / stages, 8);
+        if (piped && reduce_chunk_bytes <= 0 && warps >= 1 && warps < std::min<int64_t>(2, alone) && chunk >= 2048) {
+            chunk = chunk / 2 / 128 * 128;
+            continue;
+        }
+        if (warps < 1 && piped) {
+            // a long row leaves no room for the transfer rings: halve the chunk, and without any room left fall back
+            // to the register path
+            chunk = chunk > 128 ? std::max<int64_t>(128, chunk / 2 / 128 * 128) : 0;
+            continue;
+        }
+        c.ring.stages = stages;
+        c.ring.warps = warps < 1 ? 0 : int(warps);
+        c.reduce_stages = piped ? reduce_stages : 0;
+        c.reduce_chunk_bytes = piped ? int(chunk) : 0;
+        c.ring.smem_bytes = size_t(c.ring.warps) * stages * (pitch + 8) + size_t(fixed - 256) + size_t(pipe);
+        return c;
+    }
 }
 
 cudaError_t launch_stage(const StageParams* params, LaunchShape shape, size_t smem, cudaStream_t stream) {

@@ -346,3 +346,35 @@ def test_gate_hook_wants_pinned_host_memory():
     with pytest.raises(RuntimeError, match="pinned"):
         ext.set_test_gate(torch.zeros(2, dtype=torch.int32), 1.0)  # pageable host memory: the kernel could not poll it
     ext.set_test_gate(None)
+
+
+def test_combine_shared_memory_plan():
+    """The combine's shared-memory plan fits the CTA's limit for every geometry, always leaves the transfer warps a
+    ring of at least two stages, keeps chunks 128-byte multiples no longer than a row, and gives up the reduce
+    pipeline (register path) rather than the transfer rings when a row is very long."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    limit = 227 * 1024
+    board_and_slack = 4096  # flag board, alignment, mbarriers
+    for hidden in (256, 512, 2048, 4096, 7168, 8192, 16384, 32768, 49152):
+        for parts in (1, 2, 4, 8, 16, 32):
+            for stages in (0, 2, 4):
+                warps, ring_stages, smem, r_stages, chunk = ext.combine_plan(hidden, parts, limit, stages, 0)
+                pitch = (hidden * 2 + 127) // 128 * 128
+                assert 1 <= warps <= 8 and ring_stages in (2, 3), (hidden, parts, stages, warps, ring_stages)
+                assert smem + 256 <= limit, (hidden, parts, stages, smem)
+                assert smem >= warps * ring_stages * (pitch + 8) + r_stages * parts * chunk
+                assert smem <= warps * ring_stages * (pitch + 8) + r_stages * parts * chunk + board_and_slack
+                if r_stages:
+                    assert r_stages == stages and chunk % 128 == 0 and 128 <= chunk <= pitch
+                else:
+                    assert chunk == 0
+                if stages == 0:
+                    assert r_stages == 0
+    # the headline geometry: whole-row... two stages of half-row chunks of all eight partitions, four transfer warps
+    assert ext.combine_plan(7168, 8, limit, 2, 0) == (4, 2, ext.combine_plan(7168, 8, limit, 2, 0)[2], 2, 7168)
+    # a named chunk is rounded up to 128 bytes
+    assert ext.combine_plan(7168, 8, limit, 4, 1700)[4] == 1792
+    # a row that leaves no room for a pipeline falls back to the register path instead of failing
+    assert ext.combine_plan(49152, 8, limit, 2, 0)[3] in (0, 2)
