@@ -29,6 +29,19 @@ def launch_path(request):
     ext.set_fused_limits(*before)
 
 
+@pytest.fixture(params=["reduce_default", "reduce_in_registers", "reduce_ring_small_chunks"])
+def reduce_path(request):
+    """Run a test with each form of the combine's source-side sum: the default (two-stage shared-memory ring), the
+    register path with two warps per token, and a four-stage ring with 128-byte chunks (many chunks per token)."""
+    from nanoep_b200.utils.build import load_extension
+
+    ext = load_extension()
+    setting = {"reduce_default": 0, "reduce_in_registers": 2, "reduce_ring_small_chunks": -4001}[request.param]
+    ext.set_combine_trace(False, 0, setting)
+    yield request.param
+    ext.set_combine_trace(False, 0, 0)
+
+
 def _to_cuda(ts):
     return [t.cuda() for t in ts]
 
@@ -78,6 +91,31 @@ def test_dispatch_layouts(world, kind):
                             got[r], case.xs, case.indices, case.weights, case.num_experts, r,
                             expand=expand, alignment=alignment, zero_padding=True, weighted=weighted,
                         )
+
+
+@pytest.mark.parametrize("world,multiple", [(2, False), (4, True)])
+def test_combine_reduce_paths_bit_exact(world, multiple, reduce_path):
+    """Every form of the source-side sum gives the oracle's bits (same order of FP32 additions, one rounding)."""
+    for kind in ("mixed", "masked", "skew"):
+        case = make_case(world, kind=kind, seed=21, hidden=768, tokens=37)
+        cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+        values = _choice_values(case, seed=5)
+        with EmulatedGroup(world, cfg, allow_multiple_reduction=multiple) as group:
+            for expand in (False, True):
+                got = group.dispatch(_to_cuda(case.xs), topk_idx=_to_cuda(case.indices), weights=_to_cuda(case.weights),
+                                     do_expand=expand, alignment=4, zero_padding=False)
+                torch.cuda.synchronize()
+                ys = [_expert_outputs(values, got[r], expand).cuda() for r in range(world)]
+                biases = [torch.randn(idx.shape[0], case.hidden).to(torch.bfloat16).cuda() for idx in case.indices]
+                back = group.combine(ys, [g.handle for g in got], weights=[g.topk_weights for g in got], bias=biases)
+                torch.cuda.synchronize()
+                group.check_status()
+                for r in range(world):
+                    want = source_reference(values[r], case.indices, r, case.num_experts, world, expand=expand,
+                                            allow_multiple_reduction=multiple, bias=biases[r].cpu())
+                    assert torch.equal(back[r].x.cpu().view(torch.int16), want.view(torch.int16)), (reduce_path, kind, expand, r)
+                    want_w = case.weights[r].masked_fill(case.indices[r] < 0, 0)
+                    torch.testing.assert_close(back[r].topk_weights.cpu(), want_w, rtol=0, atol=0)
 
 
 @pytest.mark.parametrize("world,multiple", [(1, False), (2, False), (2, True), (8, False), (8, True)])
