@@ -828,9 +828,9 @@ __device__ void combine_push_role(const CombineParams& p, char* smem, FlagBoard*
     const SourceWalk walk = make_walk(p.recv_rank_prefix, p.c.rank, R);
     // The walk is shared by all transfer warps of the rank: a warp takes the next position from one counter when it
     // needs work (the request for the position after that is already in flight).  Rows differ in how many transfers
-    // they need (0 to K local slots), so equal shares of rows would leave the warps with the most slots working
-    // alone at the end - with 44 transfers per warp on average the fullest of 740 warps has ~30 % more - while the
-    // links idle; with a shared position all warps end within one row of each other and rows leave in walk order.
+    // they need (0 to K local slots), so equal shares of rows leave the warps with the most slots working alone at
+    // the end; with a shared position all warps end within one row of each other and rows leave in walk order
+    // (measured at 2 GPUs and 4096 tokens per rank: the transfer warps end 8 us earlier).
     int* work = ctrl_words(p.c) + WindowLayout::kWorkCursor;
     int claimed = 0;  // lane 0: the position requested last
     auto request = [&]() {
