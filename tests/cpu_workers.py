@@ -64,6 +64,33 @@ def all_kinds(rank, world, multiple):
     return True
 
 
+def geometry_sweep(rank, world):
+    """Edge geometries against the oracle: one expert per rank, top-1, more choices than local experts, a rank
+    without tokens, both layouts, both reduction modes, alignment larger than any expert's count."""
+    checked = 0
+    for seed, (experts_per_rank, topk, tokens, hidden, kind) in enumerate([
+        (1, 1, 5, 256, "random"), (1, 2, 9, 256, "mixed"), (2, 4, 17, 512, "random"), (5, 6, 33, 256, "skew"),
+        (3, 1, 1, 256, "random"), (4, 8, 12, 256, "empty"), (2, 3, 6, 256, "masked"),
+    ]):
+        case = make_case(world, kind=kind, seed=40 + seed, hidden=hidden, tokens=tokens, experts_per_rank=experts_per_rank, topk=topk)
+        cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+        for multiple in (False, True):
+            with CpuBuffer(dist.group.WORLD, cfg, allow_multiple_reduction=multiple) as buf:
+                for expand, alignment in ((False, 1), (True, 1), (True, 16)):
+                    got = buf.dispatch(case.xs[rank], topk_idx=case.indices[rank], weights=case.weights[rank],
+                                       do_expand=expand, alignment=alignment, zero_padding=True)
+                    assert_dispatch_matches(got, case.xs, case.indices, case.weights, case.num_experts, rank,
+                                            expand=expand, alignment=alignment, zero_padding=True)
+                    values = _choice_values(case, world)
+                    back = buf.combine(_expert_outputs(values, got, expand), got.handle)
+                    want = source_reference(values[rank], case.indices, rank, case.num_experts, world, expand=expand,
+                                            allow_multiple_reduction=multiple)
+                    assert torch.equal(back.x.view(torch.int16), want.view(torch.int16)), (seed, multiple, expand, alignment)
+                    assert back.topk_weights is None
+                    checked += 1
+    return checked
+
+
 def special_bits(rank, world):
     """Dispatch moves bits: NaN payloads, infinities, negative zero and denormals arrive unchanged."""
     case = make_case(world, kind="random", seed=3, hidden=64, tokens=9)

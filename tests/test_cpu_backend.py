@@ -16,6 +16,11 @@ def test_all_kinds_against_oracle(world, multiple):
     assert all(run_gloo(world, cpu_workers.all_kinds, multiple, timeout=300))
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_edge_geometries_against_oracle(world):
+    assert run_gloo(world, cpu_workers.geometry_sweep, timeout=300) == [42] * world
+
+
 def test_special_bit_patterns_are_moved_unchanged():
     assert all(run_gloo(2, cpu_workers.special_bits))
 

@@ -118,6 +118,36 @@ def test_combine_reduce_paths_bit_exact(world, multiple, reduce_path):
                     torch.testing.assert_close(back[r].topk_weights.cpu(), want_w, rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_edge_geometries_bit_exact(world):
+    """One expert per rank, top-1, more choices than local experts, a rank without tokens, all-masked routing, an
+    alignment larger than any expert's count: dispatch and combine against the oracle, both reduction modes."""
+    for seed, (experts_per_rank, topk, tokens, hidden, kind) in enumerate([
+        (1, 1, 5, 256, "random"), (1, 2, 9, 256, "mixed"), (2, 4, 17, 512, "random"), (5, 6, 33, 256, "skew"),
+        (3, 1, 1, 256, "random"), (4, 8, 12, 256, "empty"), (2, 3, 6, 256, "masked"),
+    ]):
+        case = make_case(world, kind=kind, seed=40 + seed, hidden=hidden, tokens=tokens, experts_per_rank=experts_per_rank, topk=topk)
+        cfg = EPConfig(case.num_experts, case.num_topk, case.hidden, case.capacity)
+        values = _choice_values(case, seed=3)
+        for multiple in (False, True):
+            with EmulatedGroup(world, cfg, allow_multiple_reduction=multiple) as group:
+                for expand, alignment in ((False, 1), (True, 1), (True, 16)):
+                    got = group.dispatch(_to_cuda(case.xs), topk_idx=_to_cuda(case.indices), weights=_to_cuda(case.weights),
+                                         do_expand=expand, alignment=alignment, zero_padding=True)
+                    torch.cuda.synchronize()
+                    for r in range(world):
+                        assert_dispatch_matches(got[r], case.xs, case.indices, case.weights, case.num_experts, r,
+                                                expand=expand, alignment=alignment, zero_padding=True)
+                    ys = [_expert_outputs(values, got[r], expand).cuda() for r in range(world)]
+                    back = group.combine(ys, [g.handle for g in got])
+                    torch.cuda.synchronize()
+                    group.check_status()
+                    for r in range(world):
+                        want = source_reference(values[r], case.indices, r, case.num_experts, world, expand=expand,
+                                                allow_multiple_reduction=multiple)
+                        assert torch.equal(back[r].x.cpu().view(torch.int16), want.view(torch.int16)), (seed, multiple, expand, alignment, r)
+
+
 @pytest.mark.parametrize("world,multiple", [(1, False), (2, False), (2, True), (8, False), (8, True)])
 def test_combine_modes_bit_exact(world, multiple, launch_path):
     for kind in ("mixed", "masked", "empty", "skew"):
