@@ -580,6 +580,8 @@ def run_ours(args, rank, world, device, control_group):
             "value_formula": "(sum_ranks N_dedup_rows + combine_rows) * hidden * 2 B / max_rank device time",
             "value_uses": "mean: the sum of the timed steps' device times (max over ranks) / steps; step_ms_percentiles gives the spread",
             "host": "Python cyclic GC off inside the timed regions",
+            "combine_knobs": {"NANOEP_COMBINE_REDUCE_GROUP": os.environ.get("NANOEP_COMBINE_REDUCE_GROUP", "default (-2000: two-stage shared-memory ring)"),
+                              "NANOEP_COMBINE_STORE_DEPTH": os.environ.get("NANOEP_COMBINE_STORE_DEPTH", "default (2)")},
         },
         "dispatch_us": disp_us,
         "combine_us": comb_us,
